@@ -1,0 +1,157 @@
+/*
+ * vafa.h -- C ABI of libvafa_b200.so: packed variable-length attention and absorbed
+ * target attention for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes, enqueues its kernels on the CUDA
+ * stream it is given and returns immediately: 0 on success, a negative VAFA_ERR_* code
+ * otherwise (text via vafa_last_error()).  Unless a comment says otherwise an entry
+ * point never allocates or frees device memory and never synchronises; scratch memory is
+ * a caller-owned workspace whose size the matching *_workspace_bytes() function returns.
+ *
+ * Each declaration names the reference interface it stands in for (paths are relative to
+ * the reference project root).
+ */
+#ifndef VAFA_H_
+#define VAFA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VAFA_ABI_VERSION 1
+
+enum vafa_dtype { VAFA_F32 = 0, VAFA_BF16 = 1, VAFA_F16 = 2 };
+
+enum vafa_impl {
+  VAFA_IMPL_AUTO = 0,    /* tcgen05 kernels when the shape is supported, else the SIMT kernels */
+  VAFA_IMPL_SIMT = 1,    /* scalar CUDA kernels: any dtype, any head dim up to 512 */
+  VAFA_IMPL_TCGEN05 = 2  /* tcgen05/TMA kernels only; unsupported shapes return VAFA_ERR_UNSUPPORTED */
+};
+
+enum vafa_error {
+  VAFA_OK = 0,
+  VAFA_ERR_INVALID = -1,     /* bad argument (null pointer, bad size, misaligned base) */
+  VAFA_ERR_UNSUPPORTED = -2, /* shape or dtype the requested implementation does not cover */
+  VAFA_ERR_WORKSPACE = -3,   /* workspace missing or too small */
+  VAFA_ERR_CUDA = -4,        /* a CUDA runtime / driver call failed */
+  VAFA_ERR_DEVICE = -5       /* a kernel reported an error through the status word */
+};
+
+typedef void* vafa_stream_t; /* a cudaStream_t */
+
+/* Status word layout (4 x int32 in device memory, caller-zeroed once; kernels only ever
+ * write non-zero codes): [0] error code (0 = none), [1] kernel/site id, [2] detail (e.g. the
+ * work item), [3] reserved.  vafa_check_status() reads it after the caller has synchronised. */
+#define VAFA_STATUS_WORDS 4
+
+/* ---------------------------------------------------------------------------------------
+ * Packed variable-length attention.
+ * Stands in for _PackedVarlenAttnFunction.forward / .backward
+ * (triton_fa_varlen_v2/triton_fa_varlen_v2/interface.py:155-250 and :253-341) together with
+ * the host index builders it calls (triton_fa_varlen_v2/triton_fa_varlen_v2/chunk_indices.py:
+ * 25-75, 144-287), which here run on the device inside the call.
+ * ------------------------------------------------------------------------------------- */
+typedef struct vafa_varlen_args {
+  /* tensors, row-major contiguous: q/o/do/dq [T_q, H, D]; k/v/dk/dv [T_k, H, D] */
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;              /* forward: written; backward: read */
+  float* lse;           /* [T_q, H] fp32, log2 domain with the scale folded in:
+                           lse = m + log2(sum exp2(s - m)), s = q.k * scale * log2(e).
+                           forward: written; backward: read.  -inf for rows that see no key */
+  const void* d_o;      /* backward only */
+  void* dq;             /* backward only */
+  void* dk;             /* backward only */
+  void* dv;             /* backward only */
+  const int32_t* cu_seqlens_q; /* device, [n_seg + 1] */
+  const int32_t* cu_seqlens_k; /* device, [n_seg + 1] */
+  int32_t n_seg;
+  int32_t total_q;      /* T_q */
+  int32_t total_k;      /* T_k */
+  int32_t num_heads;    /* H */
+  int32_t head_dim;     /* D in {16, 32, 64, 128, 256} */
+  int32_t dtype;        /* enum vafa_dtype, shared by q/k/v/o/do/dq/dk/dv */
+  int32_t causal;       /* 0: every key of the segment; 1: bottom-right aligned causal mask */
+  float scale;          /* softmax scale (the caller resolves the 1/sqrt(D) default) */
+  int32_t impl;         /* enum vafa_impl */
+  int32_t split_k_block;/* 0: split factor picked from KV length and SM count;
+                           >0: fixed KV slice length (multiple of 128), like the reference's 4096 */
+  int32_t sm_count;     /* 0: query the current device */
+  void* workspace;      /* device scratch, >= vafa_varlen_*_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+  int32_t* status;      /* device, VAFA_STATUS_WORDS int32, may be NULL */
+} vafa_varlen_args;
+
+size_t vafa_varlen_fwd_workspace_bytes(const vafa_varlen_args* a);
+size_t vafa_varlen_bwd_workspace_bytes(const vafa_varlen_args* a);
+int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream);
+int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Absorbed ragged target attention (u = q_raw W_Q W_K^T per head, attend over raw X,
+ * project with W_V).
+ * Stands in for packed_target_attn's torch prologue
+ * (triton_target_attn_absorb/triton_target_attn_absorb/interface.py:434-435) and its autograd,
+ * plus _TargetAttnFunction.forward / .backward (same file :153-223 and :226-321).
+ * ------------------------------------------------------------------------------------- */
+typedef struct vafa_absorb_args {
+  const void* q_raw;    /* [T_q, d_q] */
+  const void* x;        /* [T_k, d_kv] */
+  const void* w_q;      /* [d_q, H, D_H] */
+  const void* w_k;      /* [d_kv, H, D_H] */
+  const void* w_v;      /* [d_kv, H, D_H] */
+  void* o;              /* [T_q, H, D_H]; forward: written; backward: read */
+  float* lse;           /* [T_q, H] fp32, log2 domain (as above) */
+  void* saved;          /* caller-owned buffer of vafa_absorb_saved_bytes(): written by the
+                           forward, read by the backward of the same inputs */
+  const void* d_o;      /* backward: [T_q, H, D_H] */
+  void* dq_raw;         /* backward outputs, I/O dtype, same shapes as the inputs */
+  void* dx;
+  float* dw;            /* backward: fp32 [dW_Q | dW_K | dW_V] flat, (d_q + 2 d_kv) * H * D_H floats;
+                           kept fp32 so that a data-parallel caller can sum it across ranks before
+                           rounding */
+  const int32_t* cu_seqlens_q;
+  const int32_t* cu_seqlens_k;
+  int32_t n_seg, total_q, total_k;
+  int32_t d_q, d_kv, num_heads, head_dim; /* head_dim = D_H */
+  int32_t dtype;
+  float scale;
+  int32_t impl;
+  int32_t sm_count;
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t* status;
+} vafa_absorb_args;
+
+size_t vafa_absorb_saved_bytes(const vafa_absorb_args* a);
+size_t vafa_absorb_fwd_workspace_bytes(const vafa_absorb_args* a);
+size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a);
+int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream);
+int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream);
+
+/* Inner entry on a pre-projected u [T_q, H, d_kv] (q_raw = u, w_q/w_k unused): stands in for
+ * target_attn_inner (triton_target_attn_absorb/triton_target_attn_absorb/interface.py:324-354).
+ * Backward writes du into dq_raw ([T_q, H, d_kv]), dX into dx and fp32 dW_V into dw. */
+int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream);
+int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream);
+
+/* Round an fp32 buffer to the I/O dtype: dst[i] = (dtype) src[i].  Used after the weight
+ * gradients have been summed across ranks.  Replaces the torch casts at
+ * triton_target_attn_absorb/triton_target_attn_absorb/interface.py:318-319. */
+int vafa_cast_from_f32(const float* src, void* dst, size_t n, int32_t dtype, vafa_stream_t stream);
+
+/* ---- housekeeping ------------------------------------------------------------------ */
+int vafa_abi_version(void);
+const char* vafa_last_error(void);           /* thread-local text of the last failure */
+/* Copy the status word to the host (synchronises `stream`) and translate it: returns 0 or
+ * VAFA_ERR_DEVICE with the text available from vafa_last_error(). */
+int vafa_check_status(const int32_t* status, vafa_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VAFA_H_ */
