@@ -19,6 +19,7 @@
 
 #ifdef __cplusplus
 extern "C" {
+#pragma GCC visibility push(default)
 #endif
 
 #define VAFA_ABI_VERSION 1
@@ -152,6 +153,7 @@ const char* vafa_last_error(void);           /* thread-local text of the last fa
 int vafa_check_status(const int32_t* status, vafa_stream_t stream);
 
 #ifdef __cplusplus
+#pragma GCC visibility pop
 }
 #endif
 #endif /* VAFA_H_ */

@@ -1,0 +1,134 @@
+"""GPU parity of packed_target_attn / target_attn_inner (through the C ABI) against the CPU
+oracle (explicit K = X W_K, V = X W_V formulation) and the stored outputs of the reference
+kernels.  Cases follow triton_target_attn_absorb/triton_target_attn_absorb/test_smoke.py:2295-2338."""
+import math
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import varlenabsorbflashattn_b200 as vb
+from oracle import make_absorb_inputs, target_attn_ref_fwd_bwd, uniform_lengths, log_uniform_lengths
+from helpers import check_close, check_lse
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+from make_golden import ABSORB_CASES  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+# (q_lens, k_lens) of the reference's correctness list, production dims d_q=968, d_kv=216
+REF_CASES = {
+    "smoke": ([4], [64]),
+    "single_segment": ([7], [256]),
+    "uniform4": ([8, 8, 8, 8], [128, 128, 128, 128]),
+    "ragged_real": ([7, 8, 6, 9], [2048, 1024, 1536, 512]),
+    "k_tail": ([5, 5, 5], [123, 257, 999]),
+    "q_tail": ([33, 65, 129], [64, 64, 64]),
+    "short_k": ([1, 2, 4, 8], [1, 3, 7, 15]),
+    "nq1": ([1], [512]),
+    "empty_users": ([3, 0, 0, 5], [40, 0, 17, 9]),
+}
+
+
+def _run(ql, kl, d_q, d_kv, H, D_H, dtype, seed, x_std=0.1, w_std=0.1):
+    ins = make_absorb_inputs(ql, kl, d_q, d_kv, H, D_H, dtype, seed, x_std=x_std, w_std=w_std)
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = ins
+    g = [t.to(DEV).requires_grad_(True) for t in (q_raw, X, W_Q, W_K, W_V)]
+    O = vb.packed_target_attn(*g, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    O.backward(dO.to(DEV))
+    torch.cuda.synchronize()
+    return ins, O, [t.grad for t in g]
+
+
+def _compare(ins, O, grads, dtype):
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = ins
+    ref = target_attn_ref_fwd_bwd(q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k)
+    check_close("O", O, ref[0], dtype, scale_abs=True)
+    for name, mine, r in zip(("dq_raw", "dX", "dW_Q", "dW_K", "dW_V"), grads, ref[2:]):
+        check_close(name, mine, r, dtype, scale_abs=True)
+
+
+@pytest.mark.parametrize("name", sorted(REF_CASES))
+def test_reference_cases_fp32(name):
+    ql, kl = REF_CASES[name]
+    ins, O, grads = _run(ql, kl, 968, 216, 8, 32, torch.float32, 0)
+    _compare(ins, O, grads, torch.float32)
+
+
+@pytest.mark.parametrize("name", ["smoke", "ragged_real", "k_tail", "q_tail", "short_k", "empty_users"])
+def test_reference_cases_bf16(name):
+    ql, kl = REF_CASES[name]
+    ins, O, grads = _run(ql, kl, 968, 216, 8, 32, torch.bfloat16, 0)
+    _compare(ins, O, grads, torch.bfloat16)
+
+
+def test_benchmark_dims_bf16():
+    """d_q = d_kv = 256, H = 8, D_H = 32 with the benchmark's value distributions
+    (q_raw, X ~ N(0,1); W ~ N(0, 1/256)), a scaled-down draw of configuration 4."""
+    ql = uniform_lengths(40, 1, 16, 0)
+    kl = log_uniform_lengths(40, 8, 600, 1)
+    ins, O, grads = _run(ql, kl, 256, 256, 8, 32, torch.bfloat16, 0, x_std=1.0, w_std=None)
+    _compare(ins, O, grads, torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", sorted(ABSORB_CASES))
+def test_golden_against_reference_kernels(name, golden_dir):
+    ql, kl, d_q, d_kv, H, D_H, seed = ABSORB_CASES[name]
+    ins = make_absorb_inputs(ql, kl, d_q, d_kv, H, D_H, torch.float32, seed, x_std=0.5)
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = ins
+    g = [t.to(DEV).requires_grad_(True) for t in (q_raw, X, W_Q, W_K, W_V)]
+    O = vb.packed_target_attn(*g, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    O.backward(dO.to(DEV))
+    gold = np.load(os.path.join(golden_dir, f"absorb_{name}.npz"))
+    assert (O.detach().cpu() - torch.from_numpy(gold["O"])).abs().max().item() < 5e-5
+    for t, key in zip(g, ("dq_raw", "dX", "dW_Q", "dW_K", "dW_V")):
+        ref = torch.from_numpy(gold[key])
+        assert (t.grad.cpu() - ref).abs().max().item() < 2e-4 * max(1.0, ref.abs().max().item()), key
+
+
+def test_inner_entry_matches_full_op():
+    ql, kl = [7, 8, 6, 9], [200, 100, 150, 50]
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = make_absorb_inputs(ql, kl, 64, 48, 4, 16, torch.float32, 3, x_std=0.3)
+    d = [t.to(DEV) for t in (q_raw, X, W_Q, W_K, W_V)]
+    O_full = vb.packed_target_attn(*d, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    p = (d[0] @ d[2].reshape(64, -1)).view(-1, 4, 16)
+    u = torch.einsum("thd,khd->thk", p, d[3]).contiguous().requires_grad_(True)
+    Xg, Wg = d[1].clone().requires_grad_(True), d[4].clone().requires_grad_(True)
+    qi, ki = vb.prepare_target_attn_indices(cu_q, cu_k)
+    O_in = vb.target_attn_inner(u, Xg, Wg, cu_q, cu_k, q_chunk_indices=qi, k_chunk_indices=ki, validate=False)
+    assert (O_in - O_full).abs().max().item() < 1e-5
+    O_in.backward(dO.to(DEV))
+    # oracle for du/dX/dW_V: autograd of the absorbed formulation in fp64
+    u64 = u.detach().double().cpu().requires_grad_(True)
+    X64 = X.double().requires_grad_(True)
+    W64 = W_V.double().requires_grad_(True)
+    outs = []
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    for i in range(len(ql)):
+        s = torch.einsum("qha,ka->hqk", u64[cq[i]:cq[i + 1]], X64[ck[i]:ck[i + 1]]) / math.sqrt(16)
+        ax = torch.einsum("hqk,ka->qha", s.softmax(-1), X64[ck[i]:ck[i + 1]])
+        outs.append(torch.einsum("qha,ahd->qhd", ax, W64))
+    torch.cat(outs).backward(dO.double())
+    for name, mine, r in (("du", u.grad, u64.grad), ("dX", Xg.grad, X64.grad), ("dW_V", Wg.grad, W64.grad)):
+        check_close(name, mine, r, torch.float32, scale_abs=True)
+
+
+def test_bf16_flag_and_3d_inputs():
+    ql, kl = [4, 9], [64, 33]
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = make_absorb_inputs(ql, kl, 64, 64, 8, 32, torch.float32, 4, x_std=0.3)
+    d = [t.to(DEV) for t in (q_raw, X, W_Q, W_K, W_V)]
+    O = vb.packed_target_attn(d[0][None], d[1][None], *d[2:], q_seqinfo=torch.tensor(ql), k_seqinfo=torch.tensor(kl),
+                              bf16=True)
+    assert O.dtype == torch.bfloat16 and O.shape == (13, 8, 32)
+    ref = target_attn_ref_fwd_bwd(*[t.to(torch.bfloat16) for t in (q_raw, X, W_Q, W_K, W_V)], dO, cu_q, cu_k)[0]
+    check_close("O", O, ref, torch.bfloat16, scale_abs=True)
+
+
+def test_validation_raises_on_gpu_inputs():
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = make_absorb_inputs([3, 2], [5, 4], 32, 32, 2, 16, torch.float32, 5)
+    d = [t.to(DEV) for t in (q_raw, X, W_Q, W_K, W_V)]
+    with pytest.raises(ValueError, match="k_len > 0"):
+        vb.packed_target_attn(*d, cu_seqlens_q=cu_q, cu_seqlens_k=torch.tensor([0, 9, 9], dtype=torch.int32))

@@ -1,0 +1,93 @@
+"""Host-side argument handling of the two public wrappers (no GPU): the same exception
+types as the reference for the same mistakes."""
+import pytest
+import torch
+
+import varlenabsorbflashattn_b200 as vb
+from varlenabsorbflashattn_b200 import varlen, absorb
+
+
+def test_seqinfo_errors():
+    with pytest.raises(ValueError, match="1-D"):
+        varlen._lengths_to_cu(torch.zeros(2, 2, dtype=torch.int32))
+    with pytest.raises(ValueError, match="empty"):
+        varlen._lengths_to_cu(torch.zeros(0, dtype=torch.int32))
+    with pytest.raises(ValueError, match="negative"):
+        varlen._lengths_to_cu(torch.tensor([3, -1]))
+    with pytest.raises(ValueError, match="int32"):
+        varlen._lengths_to_cu(torch.tensor([2**31 - 1, 5], dtype=torch.int64))
+    cu = varlen._lengths_to_cu(torch.tensor([3, 0, 5]))
+    assert cu.dtype == torch.int32 and cu.tolist() == [0, 3, 3, 8]
+
+
+def test_cu_seqlens_validation():
+    with pytest.raises(ValueError, match=r"\[0\] must be 0"):
+        varlen._check_cu(torch.tensor([1, 4]), 4, "cu_seqlens_q")
+    with pytest.raises(ValueError, match="must equal total tokens"):
+        varlen._check_cu(torch.tensor([0, 4]), 5, "cu_seqlens_q")
+    with pytest.raises(ValueError, match="non-decreasing"):
+        varlen._check_cu(torch.tensor([0, 5, 4]), 4, "cu_seqlens_q")
+    with pytest.raises(ValueError, match="at least 2"):
+        varlen._check_cu(torch.tensor([0]), 0, "cu_seqlens_q")
+    vb.set_validate_cu_seqlens(False)
+    try:
+        varlen._check_cu(torch.tensor([1, 4]), 4, "cu_seqlens_q")
+    finally:
+        vb.set_validate_cu_seqlens(True)
+
+
+def test_layout_errors():
+    with pytest.raises(ValueError, match="batch=1"):
+        varlen._as_thd(torch.zeros(2, 3, 1, 16), "q")
+    with pytest.raises(ValueError, match="expected 3-D"):
+        varlen._as_thd(torch.zeros(3, 16), "q")
+    x, was4 = varlen._as_thd(torch.zeros(1, 3, 2, 16), "q")
+    assert was4 and x.shape == (3, 2, 16)
+    y, _ = varlen._as_thd(torch.zeros(3, 2, 32)[:, :, ::2], "q")
+    assert y.is_contiguous()
+
+
+def test_missing_lengths():
+    q = torch.zeros(3, 1, 16)
+    with pytest.raises(ValueError, match="cu_seqlens_q or q_seqinfo"):
+        vb.packed_varlen_attn(q, q, q)
+    with pytest.raises(ValueError, match="cu_seqlens_k or k_seqinfo"):
+        vb.packed_varlen_attn(q, q, q, cu_seqlens_q=torch.tensor([0, 3]))
+
+
+def test_cpu_tensors_refused():
+    q = torch.zeros(3, 1, 16)
+    cu = torch.tensor([0, 3], dtype=torch.int32)
+    with pytest.raises(AssertionError, match="CUDA"):
+        vb.packed_varlen_attn(q, q, q, cu_seqlens_q=cu, cu_seqlens_k=cu)
+    with pytest.raises(AssertionError, match="CUDA"):
+        vb.packed_target_attn(torch.zeros(3, 8), torch.zeros(3, 8), torch.zeros(8, 2, 16), torch.zeros(8, 2, 16),
+                              torch.zeros(8, 2, 16), cu_seqlens_q=cu, cu_seqlens_k=cu)
+
+
+def test_absorb_shape_asserts_and_env(monkeypatch):
+    cu = torch.tensor([0, 3], dtype=torch.int32)
+    with pytest.raises(AssertionError, match="W_Q"):
+        vb.packed_target_attn(torch.zeros(3, 8), torch.zeros(3, 8), torch.zeros(9, 2, 16), torch.zeros(8, 2, 16),
+                              torch.zeros(8, 2, 16), cu_seqlens_q=cu, cu_seqlens_k=cu)
+    with pytest.raises(AssertionError, match="H mismatch"):
+        vb.packed_target_attn(torch.zeros(3, 8), torch.zeros(3, 8), torch.zeros(8, 2, 16), torch.zeros(8, 3, 16),
+                              torch.zeros(8, 2, 16), cu_seqlens_q=cu, cu_seqlens_k=cu)
+    monkeypatch.setenv("TRITON_TARGET_ATTN_DX_MODE", "bogus")
+    with pytest.raises(ValueError, match="TRITON_TARGET_ATTN_DX_MODE"):
+        vb.packed_target_attn(torch.zeros(3, 8), torch.zeros(3, 8), torch.zeros(8, 2, 16), torch.zeros(8, 2, 16),
+                              torch.zeros(8, 2, 16), cu_seqlens_q=cu, cu_seqlens_k=cu)
+
+
+def test_absorb_validation():
+    with pytest.raises(ValueError, match="k_len > 0"):
+        absorb._validate(torch.tensor([0, 2, 3]), torch.tensor([0, 0, 4]), 3, 4)
+    with pytest.raises(ValueError, match="non-decreasing"):
+        absorb._validate(torch.tensor([0, 3, 2]), torch.tensor([0, 1, 4]), 2, 4)
+    absorb._validate(torch.tensor([0, 0, 3]), torch.tensor([0, 0, 4]), 3, 4)
+
+
+def test_prepare_indices_format():
+    qi, ki = vb.prepare_target_attn_indices(torch.tensor([0, 17, 17, 20]), torch.tensor([0, 130, 131, 131]))
+    assert qi.dtype == torch.int32 and qi.tolist() == [[0, 0], [0, 1], [2, 0]]
+    assert ki.tolist() == [[0, 0], [0, 1], [0, 2], [1, 0]]

@@ -1,0 +1,180 @@
+"""GPU parity of packed_varlen_attn (through the C ABI) against the CPU oracle and the stored
+outputs of the reference kernels.  Cases follow the reference's own list
+(triton_fa_varlen_v2/triton_fa_varlen_v2/test_smoke.py:222-531) plus causal, empty-segment and
+split-K cases."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import varlenabsorbflashattn_b200 as vb
+from varlenabsorbflashattn_b200 import varlen as V
+from oracle import make_varlen_inputs, varlen_attn_ref_fwd_bwd, varlen_attn_ref, config_lengths
+from helpers import check_close, check_lse, LN2
+
+sys.path.insert(0, os.path.join(os.path.dirname(__file__), "golden"))
+from make_golden import VARLEN_CASES  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+CASES = {
+    "tiny": ([7, 11], [19, 5]),
+    "cross_block": ([129, 257], [33, 130]),
+    "stage1_like": ([500, 500], [19, 800]),
+    "stage2_like": ([512, 512], [500, 500]),
+    "single_seg": ([400], [400]),
+    "block_aligned": ([256, 256], [128, 128]),
+    "ones": ([1, 1, 1, 2], [1, 2, 129, 1]),
+    "empty_q_and_k": ([5, 0, 9, 4], [12, 6, 0, 31]),
+}
+
+
+@pytest.fixture(params=["simt", "tcgen05"])
+def impl(request):
+    V.set_impl(request.param)
+    yield request.param
+    V.set_impl("auto")
+
+
+def _supported(impl, dtype, D):
+    if impl == "tcgen05":
+        return dtype in (torch.bfloat16, torch.float16) and D in (64, 128)
+    return True
+
+
+def _run(ql, kl, H, D, dtype, causal, seed=0, split=None, bwd=True):
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, H, D, dtype, seed)
+    qg, kg, vg = (t.to(DEV).requires_grad_(bwd) for t in (q, k, v))
+    o, lse = vb.packed_varlen_attn_with_lse(qg, kg, vg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+                                            causal=causal, split_k_block=split)
+    grads = None
+    if bwd:
+        o.backward(do.to(DEV))
+        grads = (qg.grad, kg.grad, vg.grad)
+    torch.cuda.synchronize()
+    return (q, k, v, do, cu_q, cu_k), o, lse, grads
+
+
+def _compare(inputs, o, lse, grads, dtype, causal):
+    q, k, v, do, cu_q, cu_k = inputs
+    ro, rlse, rdq, rdk, rdv = varlen_attn_ref_fwd_bwd(q, k, v, do, cu_q, cu_k, causal=causal)
+    check_close("o", o, ro, dtype)
+    check_lse(lse / LN2, rlse)
+    if grads is not None:
+        check_close("dq", grads[0], rdq, dtype, scale_abs=True)
+        check_close("dk", grads[1], rdk, dtype, scale_abs=True)
+        check_close("dv", grads[2], rdv, dtype, scale_abs=True)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_reference_cases_bf16(impl, name, causal):
+    ql, kl = CASES[name]
+    ins, o, lse, grads = _run(ql, kl, 4, 64, torch.bfloat16, causal)
+    _compare(ins, o, lse, grads, torch.bfloat16, causal)
+
+
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 128), (torch.float16, 64),
+                                     (torch.float32, 64), (torch.bfloat16, 32), (torch.float32, 16),
+                                     (torch.bfloat16, 256)])
+def test_dtypes_and_head_dims(impl, dtype, D):
+    if not _supported(impl, dtype, D):
+        pytest.skip("shape not covered by this kernel family")
+    ins, o, lse, grads = _run([129, 257, 3], [33, 130, 300], 2, D, dtype, False, seed=1)
+    _compare(ins, o, lse, grads, dtype, False)
+    ins, o, lse, grads = _run([130, 64, 3], [130, 64, 300], 2, D, dtype, True, seed=2)
+    _compare(ins, o, lse, grads, dtype, True)
+
+
+def test_config_c1_fp32_against_reference_kernels(golden_dir):
+    """Benchmark configuration 1: fp32, H=8, D=64, lengths 17/64/128/255, seed 0."""
+    V.set_impl("auto")
+    ql, kl, H, D, seed, _ = VARLEN_CASES["c1"]
+    ins, o, lse, _ = _run(ql, kl, H, D, torch.float32, False, seed=seed, bwd=False)
+    g = np.load(os.path.join(golden_dir, "varlen_c1.npz"))
+    assert (o.cpu() - torch.from_numpy(g["o"])).abs().max().item() < 2e-5
+    assert (lse.cpu() / LN2 - torch.from_numpy(g["lse_log2"])).abs().max().item() < 2e-5
+    ro, rlse = varlen_attn_ref(*ins[:3], ins[4], ins[5])
+    check_close("o", o, ro, torch.float32, max_abs_tol=2e-5)
+
+
+@pytest.mark.parametrize("name", ["tiny", "cross_block", "split"])
+def test_golden_fp32_with_grads(name, golden_dir):
+    V.set_impl("auto")
+    ql, kl, H, D, seed, _ = VARLEN_CASES[name]
+    ins, o, lse, grads = _run(ql, kl, H, D, torch.float32, False, seed=seed)
+    g = np.load(os.path.join(golden_dir, f"varlen_{name}.npz"))
+    assert (o.cpu() - torch.from_numpy(g["o"])).abs().max().item() < 3e-5
+    for mine, key in zip(grads, ("dq", "dk", "dv")):
+        assert (mine.cpu() - torch.from_numpy(g[key])).abs().max().item() < 1e-4, key
+
+
+def test_layout_4d_and_noncontiguous(impl):
+    ql, kl = [129, 70], [200, 70]
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 4, 64, torch.bfloat16, 3)
+    q, k, v = q.to(DEV), k.to(DEV), v.to(DEV)
+    o3 = vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    o4 = vb.packed_varlen_attn(q[None], k[None], v[None], cu_seqlens_q=cu_q.to(DEV), cu_seqlens_k=cu_k.long())
+    assert o4.shape == (1,) + o3.shape and torch.equal(o4[0], o3)
+    big = torch.zeros(q.shape[0], 4, 128, dtype=q.dtype, device=DEV)
+    big[:, :, ::2] = q
+    o5 = vb.packed_varlen_attn(big[:, :, ::2], k, v, q_seqinfo=torch.tensor(ql), k_seqinfo=torch.tensor(kl))
+    assert torch.equal(o5, o3)
+
+
+def test_no_grad_equals_grad_and_is_repeatable(impl):
+    ql, kl = [300, 45, 128], [300, 500, 128]
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 4, 64, torch.bfloat16, 4)
+    outs = []
+    for rep in range(2):
+        qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+        o = vb.packed_varlen_attn(qg, kg, vg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=True)
+        o.backward(do.to(DEV))
+        outs.append((o.detach(), qg.grad, kg.grad, vg.grad))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b), "run-to-run results differ"
+    with torch.no_grad():
+        o_ng = vb.packed_varlen_attn(q.to(DEV), k.to(DEV), v.to(DEV), cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=True)
+    assert torch.equal(o_ng, outs[0][0])
+
+
+def test_partial_grad(impl):
+    ql, kl = [64, 200], [100, 260]
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 4, 64, torch.bfloat16, 5)
+    qg = q.to(DEV).requires_grad_(True)
+    o = vb.packed_varlen_attn(qg, k.to(DEV), v.to(DEV), cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    o.backward(do.to(DEV))
+    _, _, rdq, _, _ = varlen_attn_ref_fwd_bwd(q, k, v, do, cu_q, cu_k)
+    check_close("dq", qg.grad, rdq, torch.bfloat16, scale_abs=True)
+
+
+@pytest.mark.parametrize("split", [128, 256, 4096])
+def test_split_k_invariance(impl, split):
+    """Any KV slice length gives the un-split answer (to fp32 rounding of the merge)."""
+    ql, kl = [3, 140, 1], [4500, 700, 129]
+    ins, o, lse, grads = _run(ql, kl, 2, 128, torch.bfloat16, False, seed=6, split=split)
+    _compare(ins, o, lse, grads, torch.bfloat16, False)
+    _, o0, lse0, _ = _run(ql, kl, 2, 128, torch.bfloat16, False, seed=6, split=None, bwd=False)
+    assert (o.float() - o0.float()).abs().max().item() <= 2e-2
+    assert (lse - lse0).abs().max().item() <= 1e-4
+
+
+def test_decode_like_split(impl):
+    """One query row per segment over long KV (the split-K + LSE-combine shape)."""
+    kl = [8192, 9000, 12345, 300]
+    ins, o, lse, _ = _run([1] * 4, kl, 8, 128, torch.bfloat16, False, seed=7, bwd=False)
+    ro, rlse = varlen_attn_ref(*ins[:3], ins[4], ins[5])
+    check_close("o", o, ro, torch.bfloat16)
+    check_lse(lse / LN2, rlse)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_ragged_random_causal_fwd_bwd(impl, seed):
+    """A scaled-down draw of benchmark configuration 2 (log-uniform lengths, H=16->4, D=128)."""
+    from oracle import log_uniform_lengths
+    L = log_uniform_lengths(12, 1, 700, seed)
+    ins, o, lse, grads = _run(L, L, 4, 128, torch.bfloat16, True, seed=seed)
+    _compare(ins, o, lse, grads, torch.bfloat16, True)

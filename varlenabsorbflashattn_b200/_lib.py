@@ -1,0 +1,147 @@
+"""ctypes binding of libvafa_b200.so (the C ABI declared in include/vafa.h).
+
+There is no fallback: if the shared library is missing or a call fails, a RuntimeError is
+raised.  Nothing here computes anything.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libvafa_b200.so")
+
+VAFA_F32, VAFA_BF16, VAFA_F16 = 0, 1, 2
+IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2
+IMPL_NAMES = {"auto": IMPL_AUTO, "simt": IMPL_SIMT, "tcgen05": IMPL_TCGEN05}
+STATUS_WORDS = 4
+
+DTYPE_CODE = {torch.float32: VAFA_F32, torch.bfloat16: VAFA_BF16, torch.float16: VAFA_F16}
+
+EXPORTS = (
+    "vafa_abi_version", "vafa_last_error", "vafa_check_status", "vafa_cast_from_f32",
+    "vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes", "vafa_varlen_fwd", "vafa_varlen_bwd",
+    "vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes",
+    "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
+)
+
+
+class VarlenArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("lse", C.c_void_p),
+        ("d_o", C.c_void_p), ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
+        ("n_seg", C.c_int32), ("total_q", C.c_int32), ("total_k", C.c_int32),
+        ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32),
+        ("scale", C.c_float), ("impl", C.c_int32), ("split_k_block", C.c_int32), ("sm_count", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
+class AbsorbArgs(C.Structure):
+    _fields_ = [
+        ("q_raw", C.c_void_p), ("x", C.c_void_p), ("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p),
+        ("o", C.c_void_p), ("lse", C.c_void_p), ("saved", C.c_void_p), ("d_o", C.c_void_p),
+        ("dq_raw", C.c_void_p), ("dx", C.c_void_p), ("dw", C.c_void_p),
+        ("cu_seqlens_q", C.c_void_p), ("cu_seqlens_k", C.c_void_p),
+        ("n_seg", C.c_int32), ("total_q", C.c_int32), ("total_k", C.c_int32),
+        ("d_q", C.c_int32), ("d_kv", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
+        ("dtype", C.c_int32), ("scale", C.c_float), ("impl", C.c_int32), ("sm_count", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> C.CDLL:
+    """Load the library once; raise if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m varlenabsorbflashattn_b200.build` "
+                "(there is no fallback implementation)")
+        lib = C.CDLL(LIB_PATH)
+        lib.vafa_abi_version.restype = C.c_int
+        lib.vafa_last_error.restype = C.c_char_p
+        lib.vafa_check_status.argtypes = [C.c_void_p, C.c_void_p]
+        lib.vafa_check_status.restype = C.c_int
+        lib.vafa_cast_from_f32.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int32, C.c_void_p]
+        lib.vafa_cast_from_f32.restype = C.c_int
+        for name in ("vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes"):
+            getattr(lib, name).argtypes = [C.POINTER(VarlenArgs)]
+            getattr(lib, name).restype = C.c_size_t
+        for name in ("vafa_varlen_fwd", "vafa_varlen_bwd"):
+            getattr(lib, name).argtypes = [C.POINTER(VarlenArgs), C.c_void_p]
+            getattr(lib, name).restype = C.c_int
+        for name in ("vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes"):
+            getattr(lib, name).argtypes = [C.POINTER(AbsorbArgs)]
+            getattr(lib, name).restype = C.c_size_t
+        for name in ("vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd"):
+            getattr(lib, name).argtypes = [C.POINTER(AbsorbArgs), C.c_void_p]
+            getattr(lib, name).restype = C.c_int
+        if lib.vafa_abi_version() != 1:
+            raise RuntimeError("libvafa_b200.so: ABI version mismatch; rebuild")
+        _lib = lib
+    return _lib
+
+
+def last_error() -> str:
+    return load().vafa_last_error().decode("utf-8", "replace")
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed (code {rc}): {last_error()}")
+
+
+_status = {}
+_sm_count = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32[4] that kernels write error codes into (zeroed once)."""
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def sm_count(device: torch.device) -> int:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    n = _sm_count.get(idx)
+    if n is None:
+        n = torch.cuda.get_device_properties(idx).multi_processor_count
+        _sm_count[idx] = n
+    return n
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronise the current stream and raise if a kernel reported an error."""
+    st = status_word(device)
+    rc = load().vafa_check_status(st.data_ptr(), torch.cuda.current_stream(device).cuda_stream)
+    if rc != 0:
+        msg = last_error()
+        st.zero_()
+        raise RuntimeError(f"device-side error: {msg}")
+
+
+def workspace(nbytes: int, device: torch.device) -> torch.Tensor | None:
+    if nbytes <= 0:
+        return None
+    return torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()

@@ -1,0 +1,90 @@
+// Shared helpers for libvafa_b200: dtype conversion, status word, error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/vafa.h"
+
+namespace vafa {
+
+// ---- host-side error text (thread local) --------------------------------------------
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+
+#define VAFA_CUDA_CHECK(expr)                                                              \
+  do {                                                                                     \
+    cudaError_t _e = (expr);                                                               \
+    if (_e != cudaSuccess)                                                                 \
+      return ::vafa::fail(VAFA_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                          __FILE__, __LINE__);                                             \
+  } while (0)
+
+#define VAFA_LAUNCH_CHECK(name)                                                            \
+  do {                                                                                     \
+    cudaError_t _e = cudaGetLastError();                                                   \
+    if (_e != cudaSuccess)                                                                 \
+      return ::vafa::fail(VAFA_ERR_CUDA, "launch of %s failed: %s", name, cudaGetErrorString(_e)); \
+  } while (0)
+
+// ---- device-side status word ----------------------------------------------------------
+// Kernels report failures (a wait that ran out, a bad work item) by writing a non-zero code
+// once; they never trap.  Codes: 1 = mbarrier wait ran out, 2 = bad work item, 3 = TMEM.
+__device__ __forceinline__ void report_error(int32_t* status, int code, int site, int detail) {
+  if (status != nullptr) {
+    if (atomicCAS(status, 0, code) == 0) {
+      status[1] = site;
+      status[2] = detail;
+    }
+  }
+}
+
+// ---- dtype helpers -------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float to_float(T x);
+template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+
+// Pack two floats into one 32-bit word of 16-bit values (low half = first argument).
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+static inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static inline int elem_size(int dtype) { return dtype == VAFA_F32 ? 4 : 2; }
+
+// Index of the segment that holds `row`: largest s with cu[s] <= row (cu non-decreasing, so
+// empty segments are skipped).
+__device__ __forceinline__ int find_segment(const int32_t* __restrict__ cu, int n_seg, int row) {
+  int lo = 0, hi = n_seg;  // invariant: cu[lo] <= row < cu[hi]
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (cu[mid] <= row) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+}  // namespace vafa

@@ -1,0 +1,389 @@
+// Scalar (SIMT) kernels: one warp per output row, lanes across the head dimension.
+// fp32 arithmetic throughout, no shared memory, no atomics: results are run-to-run identical.
+#include "simt_kernels.cuh"
+
+namespace vafa {
+
+namespace {
+
+constexpr int kMaxT = 16;  // head dim <= 32 * kMaxT = 512
+constexpr int kWarpsPerBlock = 4;
+
+struct SegInfo {
+  int q0, Lq, k0, Lk;
+};
+
+__device__ __forceinline__ SegInfo load_seg(const int32_t* cu_q, const int32_t* cu_k, int seg) {
+  SegInfo s;
+  s.q0 = cu_q[seg];
+  s.Lq = cu_q[seg + 1] - s.q0;
+  s.k0 = cu_k[seg];
+  s.Lk = cu_k[seg + 1] - s.k0;
+  return s;
+}
+
+// ---- forward ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_fwd_kernel(SimtAttnParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (w >= (long long)p.total_q * p.H) return;
+  const int row = (int)(w / p.H), h = (int)(w % p.H);
+  const int seg = find_segment(p.cu_q, p.n_seg, row);
+  const SegInfo s = load_seg(p.cu_q, p.cu_k, seg);
+  const int i = row - s.q0;
+  int kend = p.causal ? min(s.Lk, i + s.Lk - s.Lq + 1) : s.Lk;
+  const int nd = (p.D + 31) >> 5;
+  const float c = p.scale * kLog2e;
+
+  const T* q = (const T*)p.q + (int64_t)row * p.q_row + (int64_t)h * p.q_head;
+  const T* kb = (const T*)p.k + (int64_t)s.k0 * p.k_row + (int64_t)h * p.k_head;
+  const T* vb = (const T*)p.v + (int64_t)s.k0 * p.v_row + (int64_t)h * p.v_head;
+
+  float qr[kMaxT], acc[kMaxT];
+#pragma unroll
+  for (int t = 0; t < kMaxT; ++t) {
+    const int d = lane + 32 * t;
+    qr[t] = (t < nd && d < p.D) ? to_float(q[d]) : 0.f;
+    acc[t] = 0.f;
+  }
+  float m = -INFINITY, l = 0.f;
+  for (int j = 0; j < kend; ++j) {
+    const T* kr = kb + (int64_t)j * p.k_row;
+    const T* vr = vb + (int64_t)j * p.v_row;
+    float part = 0.f;
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) {
+      const int d = lane + 32 * t;
+      if (t < nd && d < p.D) part += qr[t] * to_float(kr[d]);
+    }
+    const float sc = warp_sum(part) * c;
+    const float m_new = fmaxf(m, sc);
+    const float corr = exp2f(m - m_new);
+    const float pr = exp2f(sc - m_new);
+    l = l * corr + pr;
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) {
+      const int d = lane + 32 * t;
+      if (t < nd && d < p.D) acc[t] = acc[t] * corr + pr * to_float(vr[d]);
+    }
+    m = m_new;
+  }
+  T* o = (T*)p.o + (int64_t)row * p.q_row + (int64_t)h * p.q_head;
+  const bool dead = (kend <= 0) || !(l > 0.f);
+  const float inv = dead ? 0.f : 1.f / l;
+#pragma unroll
+  for (int t = 0; t < kMaxT; ++t) {
+    const int d = lane + 32 * t;
+    if (t < nd && d < p.D) o[d] = from_float<T>(acc[t] * inv);
+  }
+  if (lane == 0) p.lse[(int64_t)row * p.H + h] = dead ? -INFINITY : m + log2f(l);
+}
+
+// ---- delta = rowsum(O * dO) --------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+simt_delta_kernel(const T* __restrict__ o, const T* __restrict__ d_o, float* __restrict__ delta, long long n_rows, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (w >= n_rows) return;
+  const T* a = o + w * D;
+  const T* b = d_o + w * D;
+  float part = 0.f;
+  for (int d = lane; d < D; d += 32) part += to_float(a[d]) * to_float(b[d]);
+  part = warp_sum(part);
+  if (lane == 0) delta[w] = part;
+}
+
+// ---- dQ ------------------------------------------------------------------------------------
+template <typename T, typename TDO>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_dq_kernel(SimtAttnParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (w >= (long long)p.total_q * p.H) return;
+  const int row = (int)(w / p.H), h = (int)(w % p.H);
+  const int seg = find_segment(p.cu_q, p.n_seg, row);
+  const SegInfo s = load_seg(p.cu_q, p.cu_k, seg);
+  const int i = row - s.q0;
+  int kend = p.causal ? min(s.Lk, i + s.Lk - s.Lq + 1) : s.Lk;
+  const int nd = (p.D + 31) >> 5;
+  const float c = p.scale * kLog2e;
+
+  const T* q = (const T*)p.q + (int64_t)row * p.q_row + (int64_t)h * p.q_head;
+  const TDO* dor = (const TDO*)p.d_o + (int64_t)row * p.do_row + (int64_t)h * p.do_head;
+  const T* kb = (const T*)p.k + (int64_t)s.k0 * p.k_row + (int64_t)h * p.k_head;
+  const T* vb = (const T*)p.v + (int64_t)s.k0 * p.v_row + (int64_t)h * p.v_head;
+  const float lse = p.lse[(int64_t)row * p.H + h];
+  const float dl = p.delta[(int64_t)row * p.H + h];
+  if (lse == -INFINITY) kend = 0;
+
+  float qr[kMaxT], dr[kMaxT], acc[kMaxT];
+#pragma unroll
+  for (int t = 0; t < kMaxT; ++t) {
+    const int d = lane + 32 * t;
+    const bool ok = (t < nd && d < p.D);
+    qr[t] = ok ? to_float(q[d]) : 0.f;
+    dr[t] = ok ? to_float(dor[d]) : 0.f;
+    acc[t] = 0.f;
+  }
+  for (int j = 0; j < kend; ++j) {
+    const T* kr = kb + (int64_t)j * p.k_row;
+    const T* vr = vb + (int64_t)j * p.v_row;
+    float kv[kMaxT];
+    float ps = 0.f, pd = 0.f;
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) {
+      const int d = lane + 32 * t;
+      if (t < nd && d < p.D) {
+        kv[t] = to_float(kr[d]);
+        ps += qr[t] * kv[t];
+        pd += dr[t] * to_float(vr[d]);
+      } else {
+        kv[t] = 0.f;
+      }
+    }
+    const float sc = warp_sum(ps) * c;
+    const float dp = warp_sum(pd);
+    const float pr = exp2f(sc - lse);
+    const float ds = pr * (dp - dl);
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) acc[t] += ds * kv[t];
+  }
+  T* dq = (T*)p.dq + (int64_t)row * p.q_row + (int64_t)h * p.q_head;
+#pragma unroll
+  for (int t = 0; t < kMaxT; ++t) {
+    const int d = lane + 32 * t;
+    if (t < nd && d < p.D) dq[d] = from_float<T>(acc[t] * p.scale);
+  }
+}
+
+// ---- dK, dV (or their head-summed combination when K/V rows are shared by all heads) --------
+template <typename T, typename TDO>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) simt_dkv_kernel(SimtAttnParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const long long n_units = p.shared_kv ? (long long)p.total_k : (long long)p.total_k * p.H;
+  if (w >= n_units) return;
+  const int krow = p.shared_kv ? (int)w : (int)(w / p.H);
+  const int h_first = p.shared_kv ? 0 : (int)(w % p.H);
+  const int h_last = p.shared_kv ? p.H : h_first + 1;
+  const int seg = find_segment(p.cu_k, p.n_seg, krow);
+  const SegInfo s = load_seg(p.cu_q, p.cu_k, seg);
+  const int j = krow - s.k0;
+  const int i_start = p.causal ? max(0, j - (s.Lk - s.Lq)) : 0;
+  const int nd = (p.D + 31) >> 5;
+  const float c = p.scale * kLog2e;
+
+  float tot[kMaxT];
+#pragma unroll
+  for (int t = 0; t < kMaxT; ++t) tot[t] = 0.f;
+
+  for (int h = h_first; h < h_last; ++h) {
+    const T* kr = (const T*)p.k + (int64_t)krow * p.k_row + (int64_t)h * p.k_head;
+    const T* vr = (const T*)p.v + (int64_t)krow * p.v_row + (int64_t)h * p.v_head;
+    float kreg[kMaxT], vreg[kMaxT], dka[kMaxT], dva[kMaxT];
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) {
+      const int d = lane + 32 * t;
+      const bool ok = (t < nd && d < p.D);
+      kreg[t] = ok ? to_float(kr[d]) : 0.f;
+      vreg[t] = ok ? to_float(vr[d]) : 0.f;
+      dka[t] = 0.f;
+      dva[t] = 0.f;
+    }
+    for (int i = i_start; i < s.Lq; ++i) {
+      const int row = s.q0 + i;
+      const float lse = p.lse[(int64_t)row * p.H + h];
+      if (lse == -INFINITY) continue;
+      const float dl = p.delta[(int64_t)row * p.H + h];
+      const T* q = (const T*)p.q + (int64_t)row * p.q_row + (int64_t)h * p.q_head;
+      const TDO* dor = (const TDO*)p.d_o + (int64_t)row * p.do_row + (int64_t)h * p.do_head;
+      float qv[kMaxT], dv_[kMaxT];
+      float ps = 0.f, pd = 0.f;
+#pragma unroll
+      for (int t = 0; t < kMaxT; ++t) {
+        const int d = lane + 32 * t;
+        if (t < nd && d < p.D) {
+          qv[t] = to_float(q[d]);
+          dv_[t] = to_float(dor[d]);
+          ps += qv[t] * kreg[t];
+          pd += dv_[t] * vreg[t];
+        } else {
+          qv[t] = 0.f;
+          dv_[t] = 0.f;
+        }
+      }
+      const float sc = warp_sum(ps) * c;
+      const float dp = warp_sum(pd);
+      const float pr = exp2f(sc - lse);
+      const float ds = pr * (dp - dl);
+#pragma unroll
+      for (int t = 0; t < kMaxT; ++t) {
+        dva[t] += pr * dv_[t];
+        dka[t] += ds * qv[t];
+      }
+    }
+    if (p.shared_kv) {
+#pragma unroll
+      for (int t = 0; t < kMaxT; ++t) tot[t] += dka[t] * p.scale + dva[t];
+    } else {
+      T* dk = (T*)p.dk + (int64_t)krow * p.k_row + (int64_t)h * p.k_head;
+      T* dv = (T*)p.dv + (int64_t)krow * p.v_row + (int64_t)h * p.v_head;
+#pragma unroll
+      for (int t = 0; t < kMaxT; ++t) {
+        const int d = lane + 32 * t;
+        if (t < nd && d < p.D) {
+          dk[d] = from_float<T>(dka[t] * p.scale);
+          dv[d] = from_float<T>(dva[t]);
+        }
+      }
+    }
+  }
+  if (p.shared_kv) {
+    T* dk = (T*)p.dk + (int64_t)krow * p.k_row;
+#pragma unroll
+    for (int t = 0; t < kMaxT; ++t) {
+      const int d = lane + 32 * t;
+      if (t < nd && d < p.D) dk[d] = from_float<T>(tot[t]);
+    }
+  }
+}
+
+// ---- small dense products -------------------------------------------------------------------
+template <typename TA, typename TB, typename TC>
+__global__ void __launch_bounds__(256) simt_gemm_kernel(SimtGemm g) {
+  __shared__ float As[16][17];
+  __shared__ float Bs[16][17];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int n0 = blockIdx.x * 16, m0 = blockIdx.y * 16, b = blockIdx.z;
+  const TA* A = (const TA*)g.A + (int64_t)b * g.a_b;
+  const TB* B = (const TB*)g.B + (int64_t)b * g.b_b;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < g.K; k0 += 16) {
+    const int am = m0 + ty, ak = k0 + tx;
+    As[ty][tx] = (am < g.M && ak < g.K) ? to_float(A[(int64_t)am * g.a_m + (int64_t)ak * g.a_k]) : 0.f;
+    const int bk = k0 + ty, bn = n0 + tx;
+    Bs[ty][tx] = (bk < g.K && bn < g.N) ? to_float(B[(int64_t)bk * g.b_k + (int64_t)bn * g.b_n]) : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) acc += As[ty][kk] * Bs[kk][tx];
+    __syncthreads();
+  }
+  const int m = m0 + ty, n = n0 + tx;
+  if (m < g.M && n < g.N) {
+    TC* C = (TC*)g.C + (int64_t)b * g.c_b;
+    C[(int64_t)m * g.c_m + (int64_t)n * g.c_n] = from_float<TC>(acc * g.alpha);
+  }
+}
+
+template <typename T>
+__global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) dst[i] = from_float<T>(src[i]);
+}
+
+inline unsigned warp_grid(long long n_warps) {
+  return (unsigned)((n_warps + kWarpsPerBlock - 1) / kWarpsPerBlock);
+}
+
+}  // namespace
+
+#define DISPATCH_T(dtype, ...)                                          \
+  switch (dtype) {                                                      \
+    case VAFA_F32: { using T = float; __VA_ARGS__; break; }             \
+    case VAFA_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; }    \
+    case VAFA_F16: { using T = __half; __VA_ARGS__; break; }            \
+    default: return fail(VAFA_ERR_INVALID, "unknown dtype %d", dtype);  \
+  }
+
+int simt_attn_fwd(const SimtAttnParams& p, cudaStream_t s) {
+  if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
+  const long long n = (long long)p.total_q * p.H;
+  if (n == 0) return 0;
+  DISPATCH_T(p.dtype, simt_fwd_kernel<T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
+  VAFA_LAUNCH_CHECK("simt_fwd_kernel");
+  return 0;
+}
+
+int simt_attn_delta(const void* o, const void* d_o, float* delta, int rows, int H, int D, int dtype, cudaStream_t s) {
+  const long long n = (long long)rows * H;
+  if (n == 0) return 0;
+  DISPATCH_T(dtype, simt_delta_kernel<T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>((const T*)o, (const T*)d_o, delta, n, D));
+  VAFA_LAUNCH_CHECK("simt_delta_kernel");
+  return 0;
+}
+
+int simt_attn_dq(const SimtAttnParams& p, cudaStream_t s) {
+  if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
+  const long long n = (long long)p.total_q * p.H;
+  if (n == 0) return 0;
+  if (p.do_f32) {
+    DISPATCH_T(p.dtype, simt_dq_kernel<T, float><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
+  } else {
+    DISPATCH_T(p.dtype, simt_dq_kernel<T, T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
+  }
+  VAFA_LAUNCH_CHECK("simt_dq_kernel");
+  return 0;
+}
+
+int simt_attn_dkv(const SimtAttnParams& p, cudaStream_t s) {
+  if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
+  const long long n = p.shared_kv ? (long long)p.total_k : (long long)p.total_k * p.H;
+  if (n == 0) return 0;
+  if (p.do_f32) {
+    DISPATCH_T(p.dtype, simt_dkv_kernel<T, float><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
+  } else {
+    DISPATCH_T(p.dtype, simt_dkv_kernel<T, T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
+  }
+  VAFA_LAUNCH_CHECK("simt_dkv_kernel");
+  return 0;
+}
+
+namespace {
+template <typename TA, typename TB>
+int gemm_c(const SimtGemm& g, dim3 grid, cudaStream_t s) {
+  switch (g.c_type) {
+    case VAFA_F32: simt_gemm_kernel<TA, TB, float><<<grid, 256, 0, s>>>(g); break;
+    case VAFA_BF16: simt_gemm_kernel<TA, TB, __nv_bfloat16><<<grid, 256, 0, s>>>(g); break;
+    case VAFA_F16: simt_gemm_kernel<TA, TB, __half><<<grid, 256, 0, s>>>(g); break;
+    default: return fail(VAFA_ERR_INVALID, "unknown dtype %d", g.c_type);
+  }
+  return 0;
+}
+template <typename TA>
+int gemm_b(const SimtGemm& g, dim3 grid, cudaStream_t s) {
+  switch (g.b_type) {
+    case VAFA_F32: return gemm_c<TA, float>(g, grid, s);
+    case VAFA_BF16: return gemm_c<TA, __nv_bfloat16>(g, grid, s);
+    case VAFA_F16: return gemm_c<TA, __half>(g, grid, s);
+    default: return fail(VAFA_ERR_INVALID, "unknown dtype %d", g.b_type);
+  }
+}
+}  // namespace
+
+int simt_gemm(const SimtGemm& g, cudaStream_t s) {
+  if (g.M <= 0 || g.N <= 0 || g.batch <= 0) return 0;
+  dim3 grid((g.N + 15) / 16, (g.M + 15) / 16, g.batch);
+  if (grid.y > 65535 || grid.z > 65535) return fail(VAFA_ERR_UNSUPPORTED, "simt_gemm grid too large");
+  int rc;
+  switch (g.a_type) {
+    case VAFA_F32: rc = gemm_b<float>(g, grid, s); break;
+    case VAFA_BF16: rc = gemm_b<__nv_bfloat16>(g, grid, s); break;
+    case VAFA_F16: rc = gemm_b<__half>(g, grid, s); break;
+    default: return fail(VAFA_ERR_INVALID, "unknown dtype %d", g.a_type);
+  }
+  if (rc) return rc;
+  VAFA_LAUNCH_CHECK("simt_gemm_kernel");
+  return 0;
+}
+
+int cast_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) {
+  if (n == 0) return 0;
+  const unsigned grid = (unsigned)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
+  DISPATCH_T(dtype, cast_kernel<T><<<grid, 256, 0, s>>>(src, (T*)dst, n));
+  VAFA_LAUNCH_CHECK("cast_kernel");
+  return 0;
+}
+
+}  // namespace vafa

@@ -1,0 +1,334 @@
+// C ABI of libvafa_b200.so: argument checks, implementation choice, workspace carving.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "simt_kernels.cuh"
+#include "sm100_kernels.cuh"
+
+namespace vafa {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+namespace {
+
+bool valid_dtype(int d) { return d == VAFA_F32 || d == VAFA_BF16 || d == VAFA_F16; }
+
+int check_varlen(const vafa_varlen_args* a, bool bwd) {
+  if (!a) return fail(VAFA_ERR_INVALID, "null args");
+  if (!valid_dtype(a->dtype)) return fail(VAFA_ERR_INVALID, "bad dtype %d", a->dtype);
+  if (a->n_seg < 1 || a->total_q < 0 || a->total_k < 0 || a->num_heads < 1)
+    return fail(VAFA_ERR_INVALID, "bad sizes n_seg=%d T_q=%d T_k=%d H=%d", a->n_seg, a->total_q, a->total_k, a->num_heads);
+  const int D = a->head_dim;
+  if (!(D == 16 || D == 32 || D == 64 || D == 128 || D == 256))
+    return fail(VAFA_ERR_UNSUPPORTED, "head_dim %d not supported (16/32/64/128/256)", D);
+  if (!a->cu_seqlens_q || !a->cu_seqlens_k) return fail(VAFA_ERR_INVALID, "null cu_seqlens");
+  if (a->total_q > 0 && (!a->q || !a->o || !a->lse)) return fail(VAFA_ERR_INVALID, "null q/o/lse");
+  if (a->total_k > 0 && (!a->k || !a->v)) return fail(VAFA_ERR_INVALID, "null k/v");
+  if (bwd) {
+    if (a->total_q > 0 && (!a->d_o || !a->dq)) return fail(VAFA_ERR_INVALID, "null d_o/dq");
+    if (a->total_k > 0 && (!a->dk || !a->dv)) return fail(VAFA_ERR_INVALID, "null dk/dv");
+  }
+  if (a->split_k_block < 0 || (a->split_k_block % 128) != 0)
+    return fail(VAFA_ERR_INVALID, "split_k_block %d must be 0 or a multiple of 128", a->split_k_block);
+  return 0;
+}
+
+bool varlen_fwd_tc_ok(const vafa_varlen_args* a) { return sm100_varlen_fwd_supported(a); }
+bool varlen_bwd_tc_ok(const vafa_varlen_args* a) { return sm100_varlen_bwd_supported(a); }
+
+// 0 = simt, 1 = tcgen05, <0 error
+int pick_impl(int impl, bool tc_ok, const char* what) {
+  if (impl == VAFA_IMPL_SIMT) return 0;
+  if (impl == VAFA_IMPL_TCGEN05) {
+    if (!tc_ok) return fail(VAFA_ERR_UNSUPPORTED, "%s: shape/dtype not covered by the tcgen05 kernels", what);
+    return 1;
+  }
+  if (impl != VAFA_IMPL_AUTO) return fail(VAFA_ERR_INVALID, "bad impl %d", impl);
+  return tc_ok ? 1 : 0;
+}
+
+SimtAttnParams simt_from_varlen(const vafa_varlen_args* a) {
+  SimtAttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = a->q; p.k = a->k; p.v = a->v; p.o = a->o; p.lse = a->lse;
+  p.d_o = a->d_o; p.dq = a->dq; p.dk = a->dk; p.dv = a->dv;
+  p.cu_q = a->cu_seqlens_q; p.cu_k = a->cu_seqlens_k;
+  p.n_seg = a->n_seg; p.total_q = a->total_q; p.total_k = a->total_k; p.H = a->num_heads; p.D = a->head_dim;
+  const int64_t hd = (int64_t)a->num_heads * a->head_dim;
+  p.q_row = p.k_row = p.v_row = p.do_row = hd;
+  p.q_head = p.k_head = p.v_head = p.do_head = a->head_dim;
+  p.causal = a->causal; p.scale = a->scale; p.shared_kv = 0; p.dtype = a->dtype; p.do_f32 = 0;
+  return p;
+}
+
+int need_ws(const void* ws, size_t have, size_t need) {
+  if (need == 0) return 0;
+  if (!ws || have < need) return fail(VAFA_ERR_WORKSPACE, "workspace too small: have %zu, need %zu", have, need);
+  if ((reinterpret_cast<uintptr_t>(ws) & 255) != 0) return fail(VAFA_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  return 0;
+}
+
+// ---- absorb: sizes of the pieces ---------------------------------------------------------
+struct AbsorbSizes {
+  size_t p, u, axn;               // saved (I/O dtype)
+  size_t dax, delta, du, dp;      // backward scratch
+};
+
+AbsorbSizes absorb_sizes(const vafa_absorb_args* a) {
+  AbsorbSizes z;
+  const size_t es = elem_size(a->dtype);
+  const size_t tq = (size_t)a->total_q, H = a->num_heads, dh = a->head_dim, dkv = a->d_kv;
+  z.p = align_up(tq * H * dh * es, 256);
+  z.u = align_up(tq * H * dkv * es, 256);
+  z.axn = align_up(tq * H * dkv * es, 256);
+  z.dax = align_up(tq * H * dkv * 4, 256);
+  z.delta = align_up(tq * H * 4, 256);
+  z.du = align_up(tq * H * dkv * es, 256);
+  z.dp = align_up(tq * H * dh * es, 256);
+  return z;
+}
+
+int check_absorb(const vafa_absorb_args* a, bool bwd, bool inner) {
+  if (!a) return fail(VAFA_ERR_INVALID, "null args");
+  if (!valid_dtype(a->dtype)) return fail(VAFA_ERR_INVALID, "bad dtype %d", a->dtype);
+  if (a->n_seg < 1 || a->total_q < 0 || a->total_k < 0 || a->num_heads < 1 || a->d_kv < 1 || (!inner && a->d_q < 1))
+    return fail(VAFA_ERR_INVALID, "bad sizes");
+  const int D = a->head_dim;
+  if (!(D == 16 || D == 32 || D == 64 || D == 128 || D == 256))
+    return fail(VAFA_ERR_UNSUPPORTED, "D_H %d not supported (16/32/64/128/256)", D);
+  if (a->d_kv > 512) return fail(VAFA_ERR_UNSUPPORTED, "d_kv %d > 512", a->d_kv);
+  if (!a->cu_seqlens_q || !a->cu_seqlens_k) return fail(VAFA_ERR_INVALID, "null cu_seqlens");
+  if (!a->w_v || (!inner && (!a->w_q || !a->w_k))) return fail(VAFA_ERR_INVALID, "null weights");
+  if (a->total_q > 0 && (!a->q_raw || !a->o || !a->lse || !a->saved)) return fail(VAFA_ERR_INVALID, "null q_raw/o/lse/saved");
+  if (a->total_k > 0 && !a->x) return fail(VAFA_ERR_INVALID, "null x");
+  if (bwd) {
+    if (!a->dw) return fail(VAFA_ERR_INVALID, "null dw");
+    if (a->total_q > 0 && (!a->d_o || !a->dq_raw)) return fail(VAFA_ERR_INVALID, "null d_o/dq_raw");
+    if (a->total_k > 0 && !a->dx) return fail(VAFA_ERR_INVALID, "null dx");
+  }
+  return 0;
+}
+
+// attention core of the absorb operator on the SIMT kernels: q = u [T_q,H,d_kv], k = v = X.
+SimtAttnParams simt_from_absorb(const vafa_absorb_args* a, const void* u, void* axn) {
+  SimtAttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = u; p.k = a->x; p.v = a->x; p.o = axn; p.lse = a->lse;
+  p.cu_q = a->cu_seqlens_q; p.cu_k = a->cu_seqlens_k;
+  p.n_seg = a->n_seg; p.total_q = a->total_q; p.total_k = a->total_k; p.H = a->num_heads; p.D = a->d_kv;
+  p.q_row = (int64_t)a->num_heads * a->d_kv; p.q_head = a->d_kv;
+  p.k_row = p.v_row = a->d_kv; p.k_head = p.v_head = 0;
+  p.do_row = p.q_row; p.do_head = p.q_head;
+  p.causal = 0; p.scale = a->scale; p.shared_kv = 1; p.dtype = a->dtype; p.do_f32 = 1;
+  return p;
+}
+
+int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
+  const AbsorbSizes z = absorb_sizes(a);
+  char* sv = (char*)a->saved;
+  const int H = a->num_heads, dh = a->head_dim, dkv = a->d_kv, Tq = a->total_q;
+  const void* u;
+  void* axn;
+  int rc;
+  if (inner) {
+    u = a->q_raw;
+    axn = sv;
+  } else {
+    void* p = sv;
+    void* ub = sv + z.p;
+    axn = sv + z.p + z.u;
+    // p = q_raw W_Q                      [T_q, H*D_H]
+    SimtGemm g1{a->q_raw, a->w_q, p, a->dtype, a->dtype, a->dtype, Tq, H * dh, a->d_q, 1,
+                a->d_q, 1, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
+    if ((rc = simt_gemm(g1, s))) return rc;
+    // u_h = p_h W_K_h^T                  [T_q, H, d_kv]; batch over heads
+    SimtGemm g2{p, a->w_k, ub, a->dtype, a->dtype, a->dtype, Tq, dkv, dh, H,
+                (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
+    if ((rc = simt_gemm(g2, s))) return rc;
+    u = ub;
+  }
+  SimtAttnParams p = simt_from_absorb(a, u, axn);
+  if ((rc = simt_attn_fwd(p, s))) return rc;
+  // O_h = axn_h W_V_h                    [T_q, H, D_H]; batch over heads
+  SimtGemm g3{axn, a->w_v, a->o, a->dtype, a->dtype, a->dtype, Tq, dh, dkv, H,
+              (int64_t)H * dkv, 1, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
+  return simt_gemm(g3, s);
+}
+
+int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
+  const AbsorbSizes z = absorb_sizes(a);
+  char* sv = (char*)a->saved;
+  char* ws = (char*)a->workspace;
+  const int H = a->num_heads, dh = a->head_dim, dkv = a->d_kv, Tq = a->total_q, dq = a->d_q;
+  const void* u = inner ? a->q_raw : (const void*)(sv + z.p);
+  const void* p = inner ? nullptr : (const void*)sv;
+  void* axn = inner ? (void*)sv : (void*)(sv + z.p + z.u);
+  float* dax = (float*)ws;
+  float* delta = (float*)(ws + z.dax);
+  void* du = inner ? a->dq_raw : (void*)(ws + z.dax + z.delta);
+  void* dp = ws + z.dax + z.delta + z.du;
+  float* dWQ = a->dw;
+  float* dWK = inner ? nullptr : a->dw + (size_t)dq * H * dh;
+  float* dWV = inner ? a->dw : a->dw + (size_t)(dq + dkv) * H * dh;
+  int rc;
+  // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
+  SimtGemm g1{a->d_o, a->w_v, dax, a->dtype, a->dtype, VAFA_F32, Tq, dkv, dh, H,
+              (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
+  if ((rc = simt_gemm(g1, s))) return rc;
+  if ((rc = simt_attn_delta(a->o, a->d_o, delta, Tq, H, dh, a->dtype, s))) return rc;
+  SimtAttnParams ap = simt_from_absorb(a, u, axn);
+  ap.d_o = dax; ap.delta = delta; ap.dq = du; ap.dk = a->dx; ap.dv = nullptr;
+  if ((rc = simt_attn_dq(ap, s))) return rc;
+  if ((rc = simt_attn_dkv(ap, s))) return rc;
+  // dW_V_h = axn_h^T dO_h                 fp32 [d_kv, H, D_H]
+  SimtGemm g2{axn, a->d_o, dWV, a->dtype, a->dtype, VAFA_F32, dkv, dh, Tq, H,
+              1, (int64_t)H * dkv, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
+  if ((rc = simt_gemm(g2, s))) return rc;
+  if (inner) return 0;
+  // dp_h = du_h W_K_h                     [T_q, H, D_H]
+  SimtGemm g3{du, a->w_k, dp, a->dtype, a->dtype, a->dtype, Tq, dh, dkv, H,
+              (int64_t)H * dkv, 1, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
+  if ((rc = simt_gemm(g3, s))) return rc;
+  // dW_K_h = du_h^T p_h                   fp32 [d_kv, H, D_H]
+  SimtGemm g4{du, p, dWK, a->dtype, a->dtype, VAFA_F32, dkv, dh, Tq, H,
+              1, (int64_t)H * dkv, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
+  if ((rc = simt_gemm(g4, s))) return rc;
+  // dW_Q = q_raw^T dp                     fp32 [d_q, H*D_H]
+  SimtGemm g5{a->q_raw, dp, dWQ, a->dtype, a->dtype, VAFA_F32, dq, H * dh, Tq, 1,
+              1, dq, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
+  if ((rc = simt_gemm(g5, s))) return rc;
+  // dq_raw = dp W_Q^T                     [T_q, d_q]
+  SimtGemm g6{dp, a->w_q, a->dq_raw, a->dtype, a->dtype, a->dtype, Tq, dq, H * dh, 1,
+              (int64_t)H * dh, 1, 0, 1, (int64_t)H * dh, 0, dq, 1, 0, 1.f};
+  return simt_gemm(g6, s);
+}
+
+}  // namespace
+}  // namespace vafa
+
+using namespace vafa;
+
+extern "C" {
+
+int vafa_abi_version(void) { return VAFA_ABI_VERSION; }
+const char* vafa_last_error(void) { return g_err; }
+
+size_t vafa_varlen_fwd_workspace_bytes(const vafa_varlen_args* a) {
+  if (!a) return 0;
+  if (a->impl != VAFA_IMPL_SIMT && varlen_fwd_tc_ok(a)) return sm100_varlen_fwd_workspace_bytes(a);
+  return 0;
+}
+
+size_t vafa_varlen_bwd_workspace_bytes(const vafa_varlen_args* a) {
+  if (!a) return 0;
+  if (a->impl != VAFA_IMPL_SIMT && varlen_bwd_tc_ok(a)) return sm100_varlen_bwd_workspace_bytes(a);
+  return align_up((size_t)a->total_q * a->num_heads * 4, 256);
+}
+
+int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream) {
+  int rc = check_varlen(a, false);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int impl = pick_impl(a->impl, varlen_fwd_tc_ok(a), "varlen_fwd");
+  if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_varlen_fwd_workspace_bytes(a)))) return rc;
+  if (impl == 1) return sm100_varlen_fwd(a, s);
+  return simt_attn_fwd(simt_from_varlen(a), s);
+}
+
+int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream) {
+  int rc = check_varlen(a, true);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int impl = pick_impl(a->impl, varlen_bwd_tc_ok(a), "varlen_bwd");
+  if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_varlen_bwd_workspace_bytes(a)))) return rc;
+  if (impl == 1) return sm100_varlen_bwd(a, s);
+  SimtAttnParams p = simt_from_varlen(a);
+  float* delta = (float*)a->workspace;
+  p.delta = delta;
+  if ((rc = simt_attn_delta(a->o, a->d_o, delta, a->total_q, a->num_heads, a->head_dim, a->dtype, s))) return rc;
+  if ((rc = simt_attn_dq(p, s))) return rc;
+  return simt_attn_dkv(p, s);
+}
+
+size_t vafa_absorb_saved_bytes(const vafa_absorb_args* a) {
+  if (!a) return 0;
+  const AbsorbSizes z = absorb_sizes(a);
+  return z.p + z.u + z.axn;
+}
+size_t vafa_absorb_fwd_workspace_bytes(const vafa_absorb_args* a) {
+  (void)a;
+  return 0;
+}
+size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
+  if (!a) return 0;
+  const AbsorbSizes z = absorb_sizes(a);
+  return z.dax + z.delta + z.du + z.dp;
+}
+
+int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
+  int rc = check_absorb(a, false, false);
+  if (rc) return rc;
+  const int impl = pick_impl(a->impl, false, "absorb_fwd");
+  if (impl < 0) return impl;
+  return absorb_fwd_simt(a, false, (cudaStream_t)stream);
+}
+int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
+  int rc = check_absorb(a, true, false);
+  if (rc) return rc;
+  const int impl = pick_impl(a->impl, false, "absorb_bwd");
+  if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
+  return absorb_bwd_simt(a, false, (cudaStream_t)stream);
+}
+int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
+  int rc = check_absorb(a, false, true);
+  if (rc) return rc;
+  const int impl = pick_impl(a->impl, false, "absorb_inner_fwd");
+  if (impl < 0) return impl;
+  return absorb_fwd_simt(a, true, (cudaStream_t)stream);
+}
+int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
+  int rc = check_absorb(a, true, true);
+  if (rc) return rc;
+  const int impl = pick_impl(a->impl, false, "absorb_inner_bwd");
+  if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
+  return absorb_bwd_simt(a, true, (cudaStream_t)stream);
+}
+
+int vafa_cast_from_f32(const float* src, void* dst, size_t n, int32_t dtype, vafa_stream_t stream) {
+  if (n > 0 && (!src || !dst)) return fail(VAFA_ERR_INVALID, "null pointer");
+  return cast_from_f32(src, dst, n, dtype, (cudaStream_t)stream);
+}
+
+int vafa_check_status(const int32_t* status, vafa_stream_t stream) {
+  if (!status) return 0;
+  int32_t h[VAFA_STATUS_WORDS] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpyAsync(h, status, sizeof(h), cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(VAFA_ERR_CUDA, "status read failed: %s", cudaGetErrorString(e));
+  if (h[0] == 0) return 0;
+  const char* what = h[0] == 1 ? "a bounded wait ran out" : h[0] == 2 ? "bad work item" : h[0] == 3 ? "tensor memory" : "unknown";
+  return fail(VAFA_ERR_DEVICE, "device error %d (%s) at site %d, detail %d", h[0], what, h[1], h[2]);
+}
+
+}  // extern "C"
