@@ -1,0 +1,527 @@
+// Packed variable-length attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma
+// with TMEM accumulators, online softmax in registers, split-K partials + LSE combine.
+//
+// One persistent CTA per SM, 6 warps:
+//   warps 0-3  softmax + epilogue: thread t owns query row t of the 128-row tile (TMEM lane t)
+//   warp 4     TMA producer (one lane): Q tile once per item, K and V tiles through a ring
+//   warp 5     tcgen05.mma issuer (one lane) and TMEM owner
+// TMEM (512 columns): S0 [0,128), S1 [128,256) fp32 scores, double buffered; the 16-bit
+// probabilities P overwrite the first 64 columns of their S buffer; O accumulator at [256,256+D).
+//
+// Per KV block g:  S[g&1] = Q K_g^T  ->  softmax warps read S, write P, rescale O when the
+// running maximum moved by more than 2^8  ->  O += P V_g.  S for block g+1 is issued before
+// block g's P is ready, so the tensor pipe works on the next scores while the softmax runs.
+//
+// Numerics follow the reference kernels (triton_fa_varlen_v2/triton_fa_varlen_v2/kernels.py:
+// 127-166): scores scaled by scale*log2(e) in fp32 after the dot, exp2-domain online softmax,
+// P rounded to the I/O dtype before P.V, fp32 row sums from the unrounded P, O = acc / l,
+// LSE = m + log2(l).
+#include <cuda.h>
+#include <type_traits>
+
+#include "sm100_common.cuh"
+#include "sm100_kernels.cuh"
+
+namespace vafa {
+namespace {
+
+using namespace ptx;
+
+constexpr int kFwdThreads = 192;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kSub = D / 64;                 // 64-column (128-byte) sub tiles per row
+  static constexpr int kSubBytes = 128 * 128;         // one sub tile: 128 rows x 128 B
+  static constexpr int kTileBytes = kSub * kSubBytes;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kOCol = 256;
+};
+
+template <int D>
+struct FwdSmem {
+  alignas(1024) uint8_t q[FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t k[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t v[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
+  alignas(8) uint64_t q_full, q_free;
+  uint64_t k_full[FwdCfg<D>::kStages], k_empty[FwdCfg<D>::kStages];
+  uint64_t v_full[FwdCfg<D>::kStages], v_empty[FwdCfg<D>::kStages];
+  uint64_t s_full[2], p_full[2], o_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct FwdParams {
+  void* o;
+  float* lse;
+  float* partial_o;
+  float* partial_lse;
+  const SchedHeader* header;
+  const WorkItem* items;
+  int H;
+  float scale_log2;
+  int32_t* status;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kFwdThreads, 1)
+varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                  const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  FwdSmem<D>& sm = *reinterpret_cast<FwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    mbar_init(smem_u32(&sm.q_full), 1);
+    mbar_init(smem_u32(&sm.q_free), 1);
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&sm.k_full[i]), 1);
+      mbar_init(smem_u32(&sm.k_empty[i]), 1);
+      mbar_init(smem_u32(&sm.v_full[i]), 1);
+      mbar_init(smem_u32(&sm.v_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm.s_full[i]), 1);
+      mbar_init(smem_u32(&sm.p_full[i]), 128);
+    }
+    mbar_init(smem_u32(&sm.o_done), 1);
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sm.tmem_base), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = sm.tmem_base;
+
+  const int n_items = p.header->n_items;
+  const long long total = (long long)max(n_items, 0) * p.H;
+  const int G = gridDim.x, cta = blockIdx.x;
+  if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, 100, n_items);
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t gk = 0, qi = 0;
+      bool alive = true;
+      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+        const long long idx = snake_index(pass, cta, G);
+        if (idx >= total) continue;
+        const WorkItem w = p.items[idx / p.H];
+        const int h = (int)(idx % p.H);
+        const int nb = (w.i_len + kTile - 1) / kTile;
+        if (nb == 0) continue;
+        if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(smem_u32(&sm.q_full), Cfg::kTileBytes);
+        for (int c = 0; c < Cfg::kSub; ++c)
+          tma_load_3d(smem_u32(sm.q) + c * Cfg::kSubBytes, &tmap_q, smem_u32(&sm.q_full), c * 64, h, w.o_start);
+        for (int b = 0; b < nb; ++b, ++gk) {
+          const int st = gk % S;
+          const uint32_t ph = (gk / S) & 1;
+          const int row = w.i_start + b * kTile;
+          if (!mbar_wait(smem_u32(&sm.k_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.k[st]) + c * Cfg::kSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
+          if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
+        }
+        ++qi;
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_qk = make_idesc(kFmt, 0, 0, 128, 128);
+      constexpr uint32_t idesc_pv = make_idesc(kFmt, 0, 1, 128, D);
+      uint32_t gk = 0, qi = 0;
+      bool alive = true;
+
+      auto issue_qk = [&](uint32_t g, bool last) -> bool {
+        const int st = g % S;
+        const uint32_t ph = (g / S) & 1;
+        if (!mbar_wait(smem_u32(&sm.k_full[st]), ph, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t d_tmem = tbase + (g & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
+          const uint64_t da = make_desc_sw128(smem_u32(sm.q) + off, 16, 1024);
+          const uint64_t db = make_desc_sw128(smem_u32(sm.k[st]) + off, 16, 1024);
+          mma_ss(d_tmem, da, db, idesc_qk, kk > 0);
+        }
+        mma_commit(smem_u32(&sm.k_empty[st]));
+        mma_commit(smem_u32(&sm.s_full[g & 1]));
+        if (last) mma_commit(smem_u32(&sm.q_free));
+        return true;
+      };
+
+      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+        const long long idx = snake_index(pass, cta, G);
+        if (idx >= total) continue;
+        const WorkItem w = p.items[idx / p.H];
+        const int nb = (w.i_len + kTile - 1) / kTile;
+        if (nb == 0) continue;
+        if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break;
+        tc_fence_after();
+        if (!issue_qk(gk, nb == 1)) break;
+        for (int b = 0; b < nb; ++b) {
+          const uint32_t g = gk + b;
+          if (b + 1 < nb) {
+            if (!issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
+          }
+          const int st = g % S;
+          const uint32_t ph = (g / S) & 1;
+          if (!mbar_wait(smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+          if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t a_tmem = tbase + (g & 1) * 128;
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk) {
+            // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart
+            const uint64_t db = make_desc_sw128(smem_u32(sm.v[st]) + kk * 2048, Cfg::kSubBytes, 1024);
+            mma_ts(tbase + Cfg::kOCol, a_tmem + kk * 8, db, idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&sm.v_empty[st]));
+          mma_commit(smem_u32(&sm.o_done));
+        }
+        gk += nb;
+        ++qi;
+      }
+    }
+  } else {
+    // ---------------- softmax + epilogue (warps 0-3) ----------------
+    const int r = threadIdx.x;  // row of the tile == TMEM lane
+    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+    const float c = p.scale_log2;
+    uint32_t gk = 0;
+    bool alive = true;
+    for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+      const long long idx = snake_index(pass, cta, G);
+      if (idx >= total) continue;
+      const WorkItem w = p.items[idx / p.H];
+      const int h = (int)(idx % p.H);
+      const int nb = (w.i_len + kTile - 1) / kTile;
+      const bool row_ok = r < w.o_rows;
+      float m_ref = -INFINITY, l = 0.f;
+
+      for (int b = 0; b < nb; ++b) {
+        const uint32_t g = gk + b;
+        if (!mbar_wait(smem_u32(&sm.s_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t s_addr = lane_base + (g & 1) * 128;
+        float s[128];
+        {
+          uint32_t t0[32], t1[32], t2[32], t3[32];
+          tmem_ld32(s_addr + 0, t0);
+          tmem_ld32(s_addr + 32, t1);
+          tmem_ld32(s_addr + 64, t2);
+          tmem_ld32(s_addr + 96, t3);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            s[i] = __uint_as_float(t0[i]);
+            s[32 + i] = __uint_as_float(t1[i]);
+            s[64 + i] = __uint_as_float(t2[i]);
+            s[96 + i] = __uint_as_float(t3[i]);
+          }
+        }
+        // mask: inner index jj = b*128 + i is visible iff jj < i_len and (causal) jj <= r + diag
+        const int lim_tail = w.i_len - 1 - b * kTile;
+        const int lim_diag = w.masked ? (w.diag - b * kTile) : 0x3fffffff;  // for row 0
+        if (lim_tail < kTile - 1 || lim_diag < kTile - 1) {
+          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff);
+#pragma unroll
+          for (int i = 0; i < 128; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
+        }
+        float mx = s[0];
+#pragma unroll
+        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        const float m_blk = mx * c;  // c > 0
+        float m_new = fmaxf(m_ref, m_blk);
+        const bool resc = m_new > m_ref + kRescaleThreshold;
+        if (!resc) m_new = m_ref;
+        const float alpha = resc ? ex2(m_ref - m_new) : 1.f;
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        float sum = 0.f;
+        uint32_t pk[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = ex2(fmaf(s[2 * i], c, -m_use));
+          const float p1 = ex2(fmaf(s[2 * i + 1], c, -m_use));
+          sum += p0 + p1;
+          pk[i] = pack2<T>(p0, p1);
+        }
+        l = l * alpha + sum;
+        m_ref = m_new;
+        {
+          uint32_t a0[32], a1[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { a0[i] = pk[i]; a1[i] = pk[32 + i]; }
+          tmem_st32(s_addr + 0, a0);
+          tmem_st32(s_addr + 32, a1);
+        }
+        if (b > 0) {
+          if (!mbar_wait(smem_u32(&sm.o_done), (g - 1) & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, resc)) {
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t t[32];
+              tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+              tmem_st32(lane_base + Cfg::kOCol + cc * 32, t);
+            }
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sm.p_full[g & 1]));
+      }
+      if (!alive) break;
+      gk += nb;
+
+      // ---- epilogue ----
+      if (nb > 0) {
+        if (!mbar_wait(smem_u32(&sm.o_done), (gk - 1) & 1, abort_flag)) break;
+        tc_fence_after();
+      }
+      const bool dead = (nb == 0) || !(l > 0.f);
+      const float inv_l = dead ? 0.f : 1.f / l;
+      const float lse_val = dead ? -INFINITY : m_ref + log2f(l);
+      if (w.partial < 0) {
+        const long long row = (long long)w.o_start + r;
+        T* optr = reinterpret_cast<T*>(p.o) + (row * p.H + h) * D;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t t[32];
+          if (nb > 0) {
+            tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = 0u;
+          }
+          if (row_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(optr + cc * 32);
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint4 u;
+              u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]) * inv_l, __uint_as_float(t[8 * v4 + 1]) * inv_l);
+              u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * inv_l, __uint_as_float(t[8 * v4 + 3]) * inv_l);
+              u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * inv_l, __uint_as_float(t[8 * v4 + 5]) * inv_l);
+              u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * inv_l, __uint_as_float(t[8 * v4 + 7]) * inv_l);
+              dst[v4] = u;
+            }
+          }
+        }
+        if (row_ok) p.lse[row * p.H + h] = lse_val;
+      } else {
+        const long long prow = (long long)w.partial + r;
+        float* optr = p.partial_o + (prow * p.H + h) * D;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t t[32];
+          if (nb > 0) {
+            tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = 0u;
+          }
+          if (row_ok) {
+            float4* dst = reinterpret_cast<float4*>(optr + cc * 32);
+#pragma unroll
+            for (int v4 = 0; v4 < 8; ++v4) {
+              float4 f;
+              f.x = __uint_as_float(t[4 * v4 + 0]) * inv_l;
+              f.y = __uint_as_float(t[4 * v4 + 1]) * inv_l;
+              f.z = __uint_as_float(t[4 * v4 + 2]) * inv_l;
+              f.w = __uint_as_float(t[4 * v4 + 3]) * inv_l;
+              dst[v4] = f;
+            }
+          }
+        }
+        if (row_ok) p.partial_lse[prow * p.H + h] = lse_val;
+      }
+      // the TMEM reads of O above must finish before the next item's first P.V overwrites O;
+      // that MMA is issued only after this thread's next p_full arrival, which follows in
+      // program order (tcgen05.wait::ld has completed every read).
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (sm.abort_flag != 0) {
+    if (threadIdx.x == 0) report_error(p.status, 1, 101, blockIdx.x);
+    // let copies that are still in flight land before shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) { }
+    __syncthreads();
+  }
+  if (warp == 5) tmem_dealloc(tbase, Cfg::kTmemCols);
+}
+
+// ---------------- split-K combine -------------------------------------------------------------
+// Merge the per-split partial outputs (already normalised, fp32) with their log2-domain LSE:
+//   m = max_s lse_s;  w_s = 2^(lse_s - m);  o = sum_s w_s o_s / sum_s w_s;  lse = m + log2 sum_s w_s
+// (reference: triton_fa_varlen_v2/triton_fa_varlen_v2/kernels.py:652-734).  One warp per
+// (row, head); each lane owns D/32 consecutive columns and reads them with one vector load.
+template <typename T, int D>
+__global__ void __launch_bounds__(256) varlen_combine_kernel(const SchedHeader* __restrict__ header,
+                                                             const CombineUnit* __restrict__ units,
+                                                             const float* __restrict__ partial_o,
+                                                             const float* __restrict__ partial_lse, T* __restrict__ o,
+                                                             float* __restrict__ lse, int H) {
+  constexpr int V = D / 32;  // floats per lane: 4 (D=128) or 2 (D=64)
+  const int n_units = header->n_combine;
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  for (int u = blockIdx.x; u < n_units; u += gridDim.x) {
+    const CombineUnit cu = units[u];
+    const int n_rh = cu.q_rows * H;
+    for (int rh = wib; rh < n_rh; rh += 8) {
+      const int r = rh / H, h = rh % H;
+      float m = -INFINITY;
+      for (int s = lane; s < cu.n_splits; s += 32)
+        m = fmaxf(m, partial_lse[((long long)cu.base + (long long)s * cu.q_rows + r) * H + h]);
+#pragma unroll
+      for (int o_ = 16; o_ > 0; o_ >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o_));
+      const float m_use = (m == -INFINITY) ? 0.f : m;
+      float acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = 0.f;
+      float den = 0.f;
+      for (int s = 0; s < cu.n_splits; ++s) {
+        const long long prow = (long long)cu.base + (long long)s * cu.q_rows + r;
+        const float wgt = exp2f(partial_lse[prow * H + h] - m_use);
+        den += wgt;
+        const float* src = partial_o + (prow * H + h) * D + lane * V;
+        if (V == 4) {
+          const float4 f = *reinterpret_cast<const float4*>(src);
+          acc[0] += wgt * f.x; acc[1] += wgt * f.y; acc[V - 2] += wgt * f.z; acc[V - 1] += wgt * f.w;
+        } else {
+          const float2 f = *reinterpret_cast<const float2*>(src);
+          acc[0] += wgt * f.x; acc[1] += wgt * f.y;
+        }
+      }
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      const long long row = (long long)cu.q_start + r;
+      T* dst = o + (row * H + h) * D + lane * V;
+      if (V == 4) {
+        uint2 pk;
+        pk.x = pack2<T>(acc[0] * inv, acc[1] * inv);
+        pk.y = pack2<T>(acc[V - 2] * inv, acc[V - 1] * inv);
+        *reinterpret_cast<uint2*>(dst) = pk;
+      } else {
+        *reinterpret_cast<uint32_t*>(dst) = pack2<T>(acc[0] * inv, acc[1] * inv);
+      }
+      if (lane == 0) lse[row * H + h] = den > 0.f ? m_use + log2f(den) : -INFINITY;
+    }
+  }
+}
+
+struct FwdWorkspace {
+  size_t header, items, combine, plse, po, total;
+  SchedCaps caps;
+};
+
+FwdWorkspace fwd_workspace(const vafa_varlen_args* a, int sm_count) {
+  FwdWorkspace w;
+  w.caps = sched_caps(kSchedFwd, a->total_q, a->total_k, a->n_seg, a->num_heads, sm_count, a->split_k_block);
+  w.header = 0;
+  w.items = 256;
+  w.combine = w.items + align_up((size_t)w.caps.cap_items * sizeof(WorkItem), 256);
+  w.plse = w.combine + align_up((size_t)w.caps.cap_combine * sizeof(CombineUnit), 256);
+  w.po = w.plse + align_up((size_t)w.caps.cap_rows * a->num_heads * 4, 256);
+  w.total = w.po + align_up((size_t)w.caps.cap_rows * a->num_heads * a->head_dim * 4, 256);
+  return w;
+}
+
+int resolve_sm_count(int given) {
+  if (given > 0) return given;
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return n;
+}
+
+template <typename T, int D>
+int launch_fwd(const vafa_varlen_args* a, cudaStream_t s) {
+  const int sms = resolve_sm_count(a->sm_count);
+  const FwdWorkspace ws = fwd_workspace(a, sms);
+  char* base = (char*)a->workspace;
+  SchedParams sp;
+  sp.cu_q = a->cu_seqlens_q; sp.cu_k = a->cu_seqlens_k; sp.n_seg = a->n_seg; sp.mode = kSchedFwd;
+  sp.causal = a->causal; sp.H = a->num_heads; sp.sm_count = sms; sp.split_len = a->split_k_block;
+  sp.cap_items = ws.caps.cap_items; sp.cap_combine = ws.caps.cap_combine; sp.cap_rows = ws.caps.cap_rows;
+  sp.header = (SchedHeader*)(base + ws.header);
+  sp.items = (WorkItem*)(base + ws.items);
+  sp.combine = (CombineUnit*)(base + ws.combine);
+  int rc = launch_scheduler(sp, s);
+  if (rc) return rc;
+
+  CUtensorMap tq, tk, tv;
+  if ((rc = encode_tmap_rows(&tq, a->q, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tk, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tv, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+
+  FwdParams p;
+  p.o = a->o; p.lse = a->lse;
+  p.partial_lse = (float*)(base + ws.plse);
+  p.partial_o = (float*)(base + ws.po);
+  p.header = sp.header; p.items = sp.items; p.H = a->num_heads;
+  p.scale_log2 = a->scale * kLog2e;
+  p.status = a->status;
+
+  const size_t smem = sizeof(FwdSmem<D>) + 1024;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  varlen_fwd_kernel<T, D><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
+  VAFA_LAUNCH_CHECK("varlen_fwd_kernel");
+  varlen_combine_kernel<T, D><<<2 * sms, 256, 0, s>>>(sp.header, sp.combine, p.partial_o, p.partial_lse,
+                                                      (T*)a->o, a->lse, a->num_heads);
+  VAFA_LAUNCH_CHECK("varlen_combine_kernel");
+  return 0;
+}
+
+}  // namespace
+
+bool sm100_varlen_fwd_supported(const vafa_varlen_args* a) {
+  if (!(a->dtype == VAFA_BF16 || a->dtype == VAFA_F16)) return false;
+  if (!(a->head_dim == 64 || a->head_dim == 128)) return false;
+  if (!(a->scale > 0.f)) return false;  // the row maximum is taken before scaling
+  if (a->total_q <= 0 || a->total_k <= 0) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(a->q) && al(a->k) && al(a->v) && al(a->o);
+}
+
+size_t sm100_varlen_fwd_workspace_bytes(const vafa_varlen_args* a) {
+  return fwd_workspace(a, resolve_sm_count(a->sm_count)).total;
+}
+
+int sm100_varlen_fwd(const vafa_varlen_args* a, cudaStream_t s) {
+  if (a->dtype == VAFA_BF16) {
+    return a->head_dim == 128 ? launch_fwd<__nv_bfloat16, 128>(a, s) : launch_fwd<__nv_bfloat16, 64>(a, s);
+  }
+  return a->head_dim == 128 ? launch_fwd<__half, 128>(a, s) : launch_fwd<__half, 64>(a, s);
+}
+
+}  // namespace vafa
