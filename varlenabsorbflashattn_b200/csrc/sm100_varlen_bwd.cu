@@ -1,0 +1,519 @@
+// Packed variable-length attention backward for sm_100a (tcgen05 + TMA + TMEM).
+//
+// Three kernels, no atomics, so gradients are run-to-run identical:
+//   1. preprocess: delta[t,h] = sum_d O*dO (fp32), written together with the LSE as float2
+//      pairs in a head-major array LD[h][t] = (lse, delta)  (reference: kernels.py:186-216)
+//   2. dQ kernel : one 128-row query tile per item, walks the segment's keys in 64-row blocks
+//      (reference: kernels.py:233-350)
+//   3. dKV kernel: one 128-row key tile per item, walks the segment's query rows in 64-row
+//      blocks (reference: kernels.py:367-494)
+// (paths: triton_fa_varlen_v2/triton_fa_varlen_v2/kernels.py)
+//
+// Kernels 2 and 3 are one template.  "Outer" is the 128-row tile that stays in shared memory
+// (two operands: Q,dO or K,V), "inner" the 64-row blocks streamed through a ring (K,V or Q,dO).
+// Per inner block g, with X/Y double buffered in TMEM so the next block's scores are computed
+// while the current block's element-wise work runs:
+//     X[g&1] = outerA . innerA^T        (S   = Q K^T      or  S^T  = K Q^T)
+//     Y[g&1] = outerB . innerB^T        (dP  = dO V^T     or  dP^T = V dO^T)
+//   compute warps (thread = outer row):  P = 2^(X c - lse),  dS = P (Y - delta)
+//     dQ : dS (16-bit) overwrites X;               ACC0 += dS . K_g
+//     dKV: P^T overwrites X, dS^T overwrites Y;    ACC0 += P^T . dO_g ,  ACC1 += dS^T . Q_g
+// TMEM columns: X0 [0,64) X1 [64,128) Y0 [128,192) Y1 [192,256) ACC0 [256,256+D) ACC1 [384,384+D).
+// The softmax scale multiplies dQ and dK once, in fp32, in the epilogue (reference:
+// kernels.py:336-348, :476-491).
+#include <cuda.h>
+#include <type_traits>
+
+#include "sm100_common.cuh"
+#include "sm100_kernels.cuh"
+
+namespace vafa {
+namespace {
+
+using namespace ptx;
+
+constexpr int kBwdThreads = 192;
+constexpr int kInner = 64;  // rows per inner block
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kStages = (D == 128) ? 3 : 4;
+  static constexpr int kSub = D / 64;
+  static constexpr int kOuterSubBytes = 128 * 128;   // 128 rows x 128 B
+  static constexpr int kInnerSubBytes = kInner * 128;  // 64 rows x 128 B
+  static constexpr int kOuterBytes = kSub * kOuterSubBytes;
+  static constexpr int kInnerBytes = kSub * kInnerSubBytes;
+  static constexpr uint32_t kTmemCols = 512;
+  static constexpr uint32_t kXCol = 0, kYCol = 128, kAcc0 = 256, kAcc1 = 384;
+};
+
+template <int D>
+struct BwdSmem {
+  alignas(1024) uint8_t outer_a[BwdCfg<D>::kOuterBytes];
+  alignas(1024) uint8_t outer_b[BwdCfg<D>::kOuterBytes];
+  alignas(1024) uint8_t inner_a[BwdCfg<D>::kStages][BwdCfg<D>::kInnerBytes];
+  alignas(1024) uint8_t inner_b[BwdCfg<D>::kStages][BwdCfg<D>::kInnerBytes];
+  alignas(8) uint64_t outer_full, outer_free;
+  uint64_t in_full[BwdCfg<D>::kStages], in_empty[BwdCfg<D>::kStages];
+  uint64_t xy_full[2], ds_full[2], acc_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct BwdParams {
+  void* out0;            // dQ, or dV
+  void* out1;            // unused, or dK
+  const float2* ld;      // [H][ld_stride] (lse with dead rows mapped to +inf, delta)
+  long long ld_stride;
+  const SchedHeader* header;
+  const WorkItem* items;
+  int H;
+  float scale;
+  float scale_log2;
+  int32_t* status;
+};
+
+template <typename T, int D, bool kDKV>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid_constant__ CUtensorMap tmap_outer_b,
+                  const __grid_constant__ CUtensorMap tmap_inner_a, const __grid_constant__ CUtensorMap tmap_inner_b,
+                  const BwdParams p) {
+  using Cfg = BwdCfg<D>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    mbar_init(smem_u32(&sm.outer_full), 1);
+    mbar_init(smem_u32(&sm.outer_free), 1);
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&sm.in_full[i]), 1);
+      mbar_init(smem_u32(&sm.in_empty[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm.xy_full[i]), 1);
+      mbar_init(smem_u32(&sm.ds_full[i]), 128);
+    }
+    mbar_init(smem_u32(&sm.acc_done), 1);
+    fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    prefetch_tensormap(&tmap_outer_a);
+    prefetch_tensormap(&tmap_outer_b);
+    prefetch_tensormap(&tmap_inner_a);
+    prefetch_tensormap(&tmap_inner_b);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sm.tmem_base), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = sm.tmem_base;
+
+  const int n_items = p.header->n_items;
+  const long long total = (long long)max(n_items, 0) * p.H;
+  const int G = gridDim.x, cta = blockIdx.x;
+  if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, kDKV ? 120 : 110, n_items);
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t gk = 0, qi = 0;
+      bool alive = true;
+      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+        const long long idx = snake_index(pass, cta, G);
+        if (idx >= total) continue;
+        const WorkItem w = p.items[idx / p.H];
+        const int h = (int)(idx % p.H);
+        const int nb = (w.i_len + kInner - 1) / kInner;
+        if (nb == 0) continue;
+        if (!mbar_wait(smem_u32(&sm.outer_free), (qi & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(smem_u32(&sm.outer_full), 2 * Cfg::kOuterBytes);
+        for (int c = 0; c < Cfg::kSub; ++c) {
+          tma_load_3d(smem_u32(sm.outer_a) + c * Cfg::kOuterSubBytes, &tmap_outer_a, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
+          tma_load_3d(smem_u32(sm.outer_b) + c * Cfg::kOuterSubBytes, &tmap_outer_b, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
+        }
+        for (int b = 0; b < nb; ++b, ++gk) {
+          const int st = gk % S;
+          const uint32_t ph = (gk / S) & 1;
+          const int row = w.i_start + b * kInner;
+          if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.in_full[st]), 2 * Cfg::kInnerBytes);
+          for (int c = 0; c < Cfg::kSub; ++c) {
+            tma_load_3d(smem_u32(sm.inner_a[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_a, smem_u32(&sm.in_full[st]), c * 64, h, row);
+            tma_load_3d(smem_u32(sm.inner_b[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_b, smem_u32(&sm.in_full[st]), c * 64, h, row);
+          }
+        }
+        ++qi;
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_xy = make_idesc(kFmt, 0, 0, 128, kInner);  // outer(128) x inner(64), both K-major
+      constexpr uint32_t idesc_acc = make_idesc(kFmt, 0, 1, 128, D);      // A from TMEM, B MN-major
+      uint32_t gk = 0, qi = 0;
+      bool alive = true;
+
+      auto issue_xy = [&](uint32_t g, bool last) -> bool {
+        const int st = g % S;
+        const uint32_t ph = (g / S) & 1;
+        if (!mbar_wait(smem_u32(&sm.in_full[st]), ph, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
+        const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offo = (kk >> 2) * Cfg::kOuterSubBytes + (kk & 3) * 32;
+          const uint32_t offi = (kk >> 2) * Cfg::kInnerSubBytes + (kk & 3) * 32;
+          mma_ss(x_tmem, make_desc_sw128(smem_u32(sm.outer_a) + offo, 16, 1024),
+                 make_desc_sw128(smem_u32(sm.inner_a[st]) + offi, 16, 1024), idesc_xy, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t offo = (kk >> 2) * Cfg::kOuterSubBytes + (kk & 3) * 32;
+          const uint32_t offi = (kk >> 2) * Cfg::kInnerSubBytes + (kk & 3) * 32;
+          mma_ss(y_tmem, make_desc_sw128(smem_u32(sm.outer_b) + offo, 16, 1024),
+                 make_desc_sw128(smem_u32(sm.inner_b[st]) + offi, 16, 1024), idesc_xy, kk > 0);
+        }
+        mma_commit(smem_u32(&sm.xy_full[g & 1]));
+        if (last) mma_commit(smem_u32(&sm.outer_free));
+        return true;
+      };
+
+      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+        const long long idx = snake_index(pass, cta, G);
+        if (idx >= total) continue;
+        const WorkItem w = p.items[idx / p.H];
+        const int nb = (w.i_len + kInner - 1) / kInner;
+        if (nb == 0) continue;
+        if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break;
+        tc_fence_after();
+        if (!issue_xy(gk, nb == 1)) break;
+        for (int b = 0; b < nb; ++b) {
+          const uint32_t g = gk + b;
+          if (b + 1 < nb) {
+            if (!issue_xy(g + 1, b + 2 == nb)) { alive = false; break; }
+          }
+          const int st = g % S;
+          if (!mbar_wait(smem_u32(&sm.ds_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
+          const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
+          const uint32_t acc = (b > 0) ? 1u : 0u;
+          if (!kDKV) {
+            // dQ += dS . K_g     (dS in X, 16-bit packed; K block MN-major)
+#pragma unroll
+            for (int kk = 0; kk < kInner / 16; ++kk)
+              mma_ts(tbase + Cfg::kAcc0, x_tmem + kk * 8,
+                     make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
+                     (acc | (kk > 0)) ? 1u : 0u);
+          } else {
+            // dV += P^T . dO_g ;  dK += dS^T . Q_g
+#pragma unroll
+            for (int kk = 0; kk < kInner / 16; ++kk)
+              mma_ts(tbase + Cfg::kAcc0, x_tmem + kk * 8,
+                     make_desc_sw128(smem_u32(sm.inner_b[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
+                     (acc | (kk > 0)) ? 1u : 0u);
+#pragma unroll
+            for (int kk = 0; kk < kInner / 16; ++kk)
+              mma_ts(tbase + Cfg::kAcc1, y_tmem + kk * 8,
+                     make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
+                     (acc | (kk > 0)) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&sm.in_empty[st]));
+          if (b + 1 == nb) mma_commit(smem_u32(&sm.acc_done));
+        }
+        gk += nb;
+        ++qi;
+      }
+    }
+  } else {
+    // ---------------- element-wise warps + epilogue (warps 0-3) ----------------
+    const int r = threadIdx.x;
+    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+    const float c = p.scale_log2;
+    uint32_t gk = 0, qi = 0;
+    bool alive = true;
+    for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
+      const long long idx = snake_index(pass, cta, G);
+      if (idx >= total) continue;
+      const WorkItem w = p.items[idx / p.H];
+      const int h = (int)(idx % p.H);
+      const int nb = (w.i_len + kInner - 1) / kInner;
+      const bool row_ok = r < w.o_rows;
+      const float2* ld_h = p.ld + (long long)h * p.ld_stride;
+      float my_lse = INFINITY, my_delta = 0.f;
+      if (!kDKV) {
+        if (row_ok && nb > 0) {
+          const float2 t = ld_h[w.o_start + r];
+          my_lse = t.x;
+          my_delta = t.y;
+        }
+      }
+
+      for (int b = 0; b < nb; ++b) {
+        const uint32_t g = gk + b;
+        if (!mbar_wait(smem_u32(&sm.xy_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t x_addr = lane_base + Cfg::kXCol + (g & 1) * kInner;
+        const uint32_t y_addr = lane_base + Cfg::kYCol + (g & 1) * kInner;
+        // visibility of inner index jj = b*64 + i for this thread's outer row r
+        //   dQ : jj < i_len and (causal) jj <= r + diag
+        //   dKV: jj < i_len and (causal) jj >= r + diag
+        const int lim_tail = w.i_len - 1 - b * kInner;
+        int lo = 0, hi = lim_tail;
+        if (w.masked) {
+          if (!kDKV) hi = min(hi, r + w.diag - b * kInner);
+          else lo = r + w.diag - b * kInner;
+        }
+        const bool need_mask = (hi < kInner - 1) || (lo > 0);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t xs[32], ys[32];
+          tmem_ld32(x_addr + half * 32, xs);
+          tmem_ld32(y_addr + half * 32, ys);
+          tmem_wait_ld();
+          uint32_t pp[16], dd[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int col = half * 32 + i + e;
+              float lse_v, delta_v;
+              if (kDKV) {
+                const float2 t = __ldg(&ld_h[w.i_start + b * kInner + col]);
+                lse_v = t.x;
+                delta_v = t.y;
+              } else {
+                lse_v = my_lse;
+                delta_v = my_delta;
+              }
+              float pr = ex2(fmaf(__uint_as_float(xs[i + e]), c, -lse_v));
+              float ds = pr * (__uint_as_float(ys[i + e]) - delta_v);
+              if (need_mask) {
+                const bool vis = (col >= lo) && (col <= hi);
+                pr = vis ? pr : 0.f;
+                ds = vis ? ds : 0.f;
+              }
+              pv[e] = pr;
+              dv[e] = ds;
+            }
+            pp[i >> 1] = pack2<T>(pv[0], pv[1]);
+            dd[i >> 1] = pack2<T>(dv[0], dv[1]);
+          }
+          // 32 fp32 columns become 16 packed columns: half h lands at packed columns [16h, 16h+16)
+          if (!kDKV) {
+            tmem_st16(x_addr + half * 16, dd);
+          } else {
+            tmem_st16(x_addr + half * 16, pp);
+            tmem_st16(y_addr + half * 16, dd);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&sm.ds_full[g & 1]));
+      }
+      if (!alive) break;
+      gk += nb;
+
+      // ---- epilogue ----
+      if (nb > 0) {
+        if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break;
+        tc_fence_after();
+        ++qi;
+      }
+      const long long row = (long long)w.o_start + r;
+#pragma unroll
+      for (int which = 0; which < (kDKV ? 2 : 1); ++which) {
+        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + (row * p.H + h) * D;
+        const float mul = (kDKV && which == 0) ? 1.f : p.scale;  // dV unscaled; dQ and dK scaled
+        const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t t[32];
+          if (nb > 0) {
+            tmem_ld32(lane_base + acc_col + cc * 32, t);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = 0u;
+          }
+          if (row_ok) {
+            uint4* dst = reinterpret_cast<uint4*>(optr + cc * 32);
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              uint4 u;
+              u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]) * mul, __uint_as_float(t[8 * v4 + 1]) * mul);
+              u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * mul, __uint_as_float(t[8 * v4 + 3]) * mul);
+              u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * mul, __uint_as_float(t[8 * v4 + 5]) * mul);
+              u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * mul, __uint_as_float(t[8 * v4 + 7]) * mul);
+              dst[v4] = u;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (sm.abort_flag != 0) {
+    if (threadIdx.x == 0) report_error(p.status, 1, kDKV ? 121 : 111, blockIdx.x);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) { }
+    __syncthreads();
+  }
+  if (warp == 5) tmem_dealloc(tbase, Cfg::kTmemCols);
+}
+
+// delta = rowsum(O * dO); LD[h][t] = (lse or +inf for rows that saw no key, delta).
+template <typename T, int D>
+__global__ void __launch_bounds__(256) bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+                                                             const float* __restrict__ lse, float2* __restrict__ ld,
+                                                             long long ld_stride, int total_q, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (w >= (long long)total_q * H) return;
+  const int t = (int)(w / H), h = (int)(w % H);
+  constexpr int V = D / 32;  // elements per lane: 4 or 2
+  const T* a = o + w * D + lane * V;
+  const T* b = d_o + w * D + lane * V;
+  float part = 0.f;
+  if (V == 4) {
+    const uint2 ua = *reinterpret_cast<const uint2*>(a);
+    const uint2 ub = *reinterpret_cast<const uint2*>(b);
+    const T* pa = reinterpret_cast<const T*>(&ua);
+    const T* pb = reinterpret_cast<const T*>(&ub);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+  } else {
+    const uint32_t ua = *reinterpret_cast<const uint32_t*>(a);
+    const uint32_t ub = *reinterpret_cast<const uint32_t*>(b);
+    const T* pa = reinterpret_cast<const T*>(&ua);
+    const T* pb = reinterpret_cast<const T*>(&ub);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+  }
+  part = warp_sum(part);
+  if (lane == 0) {
+    const float l = lse[w];
+    ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
+  }
+}
+
+struct BwdWorkspace {
+  size_t hdr_dq, hdr_dkv, items_dq, items_dkv, ld, total;
+  SchedCaps caps_dq, caps_dkv;
+  long long ld_stride;
+};
+
+int resolve_sm_count_bwd(int given) {
+  if (given > 0) return given;
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) return 148;
+  return n;
+}
+
+BwdWorkspace bwd_workspace(const vafa_varlen_args* a, int sms) {
+  BwdWorkspace w;
+  w.caps_dq = sched_caps(kSchedDq, a->total_q, a->total_k, a->n_seg, a->num_heads, sms, 0);
+  w.caps_dkv = sched_caps(kSchedDkv, a->total_k, a->total_q, a->n_seg, a->num_heads, sms, 0);
+  w.ld_stride = ((long long)a->total_q + 128 + 3) & ~3LL;  // padding: inner blocks read past the last row
+  w.hdr_dq = 0;
+  w.hdr_dkv = 256;
+  w.items_dq = 512;
+  w.items_dkv = w.items_dq + align_up((size_t)w.caps_dq.cap_items * sizeof(WorkItem), 256);
+  w.ld = w.items_dkv + align_up((size_t)w.caps_dkv.cap_items * sizeof(WorkItem), 256);
+  w.total = w.ld + align_up((size_t)a->num_heads * w.ld_stride * sizeof(float2), 256);
+  return w;
+}
+
+template <typename T, int D>
+int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
+  const int sms = resolve_sm_count_bwd(a->sm_count);
+  const BwdWorkspace ws = bwd_workspace(a, sms);
+  char* base = (char*)a->workspace;
+  int rc;
+
+  SchedParams sq;
+  sq.cu_q = a->cu_seqlens_q; sq.cu_k = a->cu_seqlens_k; sq.n_seg = a->n_seg; sq.mode = kSchedDq;
+  sq.causal = a->causal; sq.H = a->num_heads; sq.sm_count = sms; sq.split_len = 0;
+  sq.cap_items = ws.caps_dq.cap_items; sq.cap_combine = 0; sq.cap_rows = 0;
+  sq.header = (SchedHeader*)(base + ws.hdr_dq);
+  sq.items = (WorkItem*)(base + ws.items_dq);
+  sq.combine = nullptr;
+  if ((rc = launch_scheduler(sq, s))) return rc;
+  SchedParams sk = sq;
+  sk.mode = kSchedDkv;
+  sk.cap_items = ws.caps_dkv.cap_items;
+  sk.header = (SchedHeader*)(base + ws.hdr_dkv);
+  sk.items = (WorkItem*)(base + ws.items_dkv);
+  if ((rc = launch_scheduler(sk, s))) return rc;
+
+  float2* ld = (float2*)(base + ws.ld);
+  {
+    const long long n = (long long)a->total_q * a->num_heads;
+    bwd_preprocess_kernel<T, D><<<(unsigned)((n + 7) / 8), 256, 0, s>>>((const T*)a->o, (const T*)a->d_o, a->lse, ld,
+                                                                        ws.ld_stride, a->total_q, a->num_heads);
+    VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
+  }
+
+  CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
+  if ((rc = encode_tmap_rows(&q128, a->q, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&do128, a->d_o, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&k128, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&v128, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&q64, a->q, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&do64, a->d_o, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&k64, a->k, a->dtype, a->total_k, a->num_heads, D, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&v64, a->v, a->dtype, a->total_k, a->num_heads, D, kInner))) return rc;
+
+  BwdParams p;
+  p.ld = ld; p.ld_stride = ws.ld_stride; p.H = a->num_heads;
+  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e; p.status = a->status;
+  const size_t smem = sizeof(BwdSmem<D>) + 1024;
+
+  // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
+  p.out0 = a->dq; p.out1 = nullptr; p.header = sq.header; p.items = sq.items;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  varlen_bwd_kernel<T, D, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
+  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dQ>");
+
+  // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
+  p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  varlen_bwd_kernel<T, D, true><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
+  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
+  return 0;
+}
+
+}  // namespace
+
+bool sm100_varlen_bwd_supported(const vafa_varlen_args* a) {
+  if (!sm100_varlen_fwd_supported(a)) return false;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return al(a->d_o) && al(a->dq) && al(a->dk) && al(a->dv);
+}
+
+size_t sm100_varlen_bwd_workspace_bytes(const vafa_varlen_args* a) {
+  return bwd_workspace(a, resolve_sm_count_bwd(a->sm_count)).total;
+}
+
+int sm100_varlen_bwd(const vafa_varlen_args* a, cudaStream_t s) {
+  if (a->dtype == VAFA_BF16) {
+    return a->head_dim == 128 ? launch_bwd<__nv_bfloat16, 128>(a, s) : launch_bwd<__nv_bfloat16, 64>(a, s);
+  }
+  return a->head_dim == 128 ? launch_bwd<__half, 128>(a, s) : launch_bwd<__half, 64>(a, s);
+}
+
+}  // namespace vafa
