@@ -152,6 +152,17 @@ const char* vafa_last_error(void);           /* thread-local text of the last fa
  * VAFA_ERR_DEVICE with the text available from vafa_last_error(). */
 int vafa_check_status(const int32_t* status, vafa_stream_t stream);
 
+/* ---- optional per-kernel timing and launch counters -------------------------------------
+ * Not part of the reference's interface; it covers what the reference's developer tools do with
+ * CUDA events around each launch (triton_fa_varlen_v2/tools/profile_v2_kernels.py:52-65).
+ * Launch counters always run; event timing only after vafa_profile_enable(1) (two events per
+ * launch on the launch's stream).  vafa_profile_read() waits for the recorded events. */
+int vafa_profile_enable(int on);
+int vafa_profile_kernel_count(void);
+const char* vafa_profile_kernel_name(int id);
+int vafa_profile_read(int id, double* total_ms, long long* timed_launches, long long* all_launches);
+int vafa_profile_reset(void);
+
 #ifdef __cplusplus
 #pragma GCC visibility pop
 }

@@ -33,7 +33,10 @@ def _segment_attn(qi, ki, vi, scale: float, causal: bool):
     """qi [Lq,H,D], ki/vi [Lk,H,D] (compute dtype).  Returns o [Lq,H,D], lse [Lq,H] (natural log)."""
     Lq, H, D = qi.shape
     Lk = ki.shape[0]
-    s = torch.einsum("qhd,khd->hqk", qi, ki) * scale
+    qh = qi.transpose(0, 1).contiguous()   # [H, Lq, D], the layout the reference's oracle multiplies in
+    kh = ki.transpose(0, 1).contiguous()
+    vh = vi.transpose(0, 1).contiguous()
+    s = torch.matmul(qh, kh.transpose(-1, -2)) * scale
     if causal:
         row = torch.arange(Lq).view(Lq, 1)
         col = torch.arange(Lk).view(1, Lk)
@@ -45,7 +48,7 @@ def _segment_attn(qi, ki, vi, scale: float, causal: bool):
     l = p.sum(dim=-1, keepdim=True)
     lse = (m_safe + torch.log(l)).squeeze(-1)            # -inf where l == 0
     pn = p / torch.where(l == 0, torch.ones_like(l), l)
-    o = torch.einsum("hqk,khd->qhd", pn, vi)
+    o = torch.matmul(pn, vh).transpose(0, 1)
     return o, lse.transpose(0, 1)
 
 

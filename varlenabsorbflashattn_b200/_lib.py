@@ -26,6 +26,8 @@ EXPORTS = (
     "vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes", "vafa_varlen_fwd", "vafa_varlen_bwd",
     "vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes",
     "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
+    "vafa_profile_enable", "vafa_profile_kernel_count", "vafa_profile_kernel_name", "vafa_profile_read",
+    "vafa_profile_reset",
 )
 
 
@@ -89,6 +91,11 @@ def load() -> C.CDLL:
         for name in ("vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd"):
             getattr(lib, name).argtypes = [C.POINTER(AbsorbArgs), C.c_void_p]
             getattr(lib, name).restype = C.c_int
+        lib.vafa_profile_enable.argtypes = [C.c_int]
+        lib.vafa_profile_kernel_name.argtypes = [C.c_int]
+        lib.vafa_profile_kernel_name.restype = C.c_char_p
+        lib.vafa_profile_read.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_longlong),
+                                          C.POINTER(C.c_longlong)]
         if lib.vafa_abi_version() != 1:
             raise RuntimeError("libvafa_b200.so: ABI version mismatch; rebuild")
         _lib = lib
@@ -145,3 +152,23 @@ def workspace(nbytes: int, device: torch.device) -> torch.Tensor | None:
 
 def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+def profile_enable(on: bool) -> None:
+    load().vafa_profile_enable(1 if on else 0)
+
+
+def profile_reset() -> None:
+    load().vafa_profile_reset()
+
+
+def profile_read() -> dict:
+    """{kernel name: (total_ms over timed launches, timed launches, all launches)}; waits for the events."""
+    lib = load()
+    out = {}
+    for i in range(lib.vafa_profile_kernel_count()):
+        ms, nt, na = C.c_double(0), C.c_longlong(0), C.c_longlong(0)
+        lib.vafa_profile_read(i, C.byref(ms), C.byref(nt), C.byref(na))
+        if na.value:
+            out[lib.vafa_profile_kernel_name(i).decode()] = (ms.value, nt.value, na.value)
+    return out

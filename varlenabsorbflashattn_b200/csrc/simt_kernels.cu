@@ -1,6 +1,7 @@
 // Scalar (SIMT) kernels: one warp per output row, lanes across the head dimension.
 // fp32 arithmetic throughout, no shared memory, no atomics: results are run-to-run identical.
 #include "simt_kernels.cuh"
+#include "profile.cuh"
 
 namespace vafa {
 
@@ -301,6 +302,7 @@ int simt_attn_fwd(const SimtAttnParams& p, cudaStream_t s) {
   if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
   const long long n = (long long)p.total_q * p.H;
   if (n == 0) return 0;
+  LaunchScope scope(kKSimtFwd, s);
   DISPATCH_T(p.dtype, simt_fwd_kernel<T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
   VAFA_LAUNCH_CHECK("simt_fwd_kernel");
   return 0;
@@ -309,6 +311,7 @@ int simt_attn_fwd(const SimtAttnParams& p, cudaStream_t s) {
 int simt_attn_delta(const void* o, const void* d_o, float* delta, int rows, int H, int D, int dtype, cudaStream_t s) {
   const long long n = (long long)rows * H;
   if (n == 0) return 0;
+  LaunchScope scope(kKSimtDelta, s);
   DISPATCH_T(dtype, simt_delta_kernel<T><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>((const T*)o, (const T*)d_o, delta, n, D));
   VAFA_LAUNCH_CHECK("simt_delta_kernel");
   return 0;
@@ -318,6 +321,7 @@ int simt_attn_dq(const SimtAttnParams& p, cudaStream_t s) {
   if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
   const long long n = (long long)p.total_q * p.H;
   if (n == 0) return 0;
+  LaunchScope scope(kKSimtDq, s);
   if (p.do_f32) {
     DISPATCH_T(p.dtype, simt_dq_kernel<T, float><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
   } else {
@@ -331,6 +335,7 @@ int simt_attn_dkv(const SimtAttnParams& p, cudaStream_t s) {
   if (p.D > 32 * kMaxT) return fail(VAFA_ERR_UNSUPPORTED, "head dim %d > %d", p.D, 32 * kMaxT);
   const long long n = p.shared_kv ? (long long)p.total_k : (long long)p.total_k * p.H;
   if (n == 0) return 0;
+  LaunchScope scope(kKSimtDkv, s);
   if (p.do_f32) {
     DISPATCH_T(p.dtype, simt_dkv_kernel<T, float><<<warp_grid(n), kWarpsPerBlock * 32, 0, s>>>(p));
   } else {
@@ -367,6 +372,7 @@ int simt_gemm(const SimtGemm& g, cudaStream_t s) {
   dim3 grid((g.N + 15) / 16, (g.M + 15) / 16, g.batch);
   if (grid.y > 65535 || grid.z > 65535) return fail(VAFA_ERR_UNSUPPORTED, "simt_gemm grid too large");
   int rc;
+  LaunchScope scope(kKSimtGemm, s);
   switch (g.a_type) {
     case VAFA_F32: rc = gemm_b<float>(g, grid, s); break;
     case VAFA_BF16: rc = gemm_b<__nv_bfloat16>(g, grid, s); break;
@@ -381,6 +387,7 @@ int simt_gemm(const SimtGemm& g, cudaStream_t s) {
 int cast_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s) {
   if (n == 0) return 0;
   const unsigned grid = (unsigned)((n + 255) / 256 > 4096 ? 4096 : (n + 255) / 256);
+  LaunchScope scope(kKCast, s);
   DISPATCH_T(dtype, cast_kernel<T><<<grid, 256, 0, s>>>(src, (T*)dst, n));
   VAFA_LAUNCH_CHECK("cast_kernel");
   return 0;

@@ -1,5 +1,6 @@
 // Single-CTA scheduler kernel: see sm100_sched.cuh.
 #include "sm100_sched.cuh"
+#include "profile.cuh"
 
 namespace vafa {
 namespace {
@@ -183,6 +184,7 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
 }  // namespace
 
 int launch_scheduler(const SchedParams& p, cudaStream_t s) {
+  LaunchScope scope(kKSched, s);
   sched_kernel<<<1, kSchedThreads, 0, s>>>(p);
   VAFA_LAUNCH_CHECK("sched_kernel");
   return 0;

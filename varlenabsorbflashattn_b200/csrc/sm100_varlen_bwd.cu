@@ -26,6 +26,7 @@
 
 #include "sm100_common.cuh"
 #include "sm100_kernels.cuh"
+#include "profile.cuh"
 
 namespace vafa {
 namespace {
@@ -463,6 +464,7 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   float2* ld = (float2*)(base + ws.ld);
   {
     const long long n = (long long)a->total_q * a->num_heads;
+    LaunchScope scope(kKBwdPre, s);
     bwd_preprocess_kernel<T, D><<<(unsigned)((n + 7) / 8), 256, 0, s>>>((const T*)a->o, (const T*)a->d_o, a->lse, ld,
                                                                         ws.ld_stride, a->total_q, a->num_heads);
     VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
@@ -486,13 +488,19 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
   p.out0 = a->dq; p.out1 = nullptr; p.header = sq.header; p.items = sq.items;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  varlen_bwd_kernel<T, D, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
+  {
+    LaunchScope scope(kKBwdDq, s);
+    varlen_bwd_kernel<T, D, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
+  }
   VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dQ>");
 
   // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
   p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  varlen_bwd_kernel<T, D, true><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
+  {
+    LaunchScope scope(kKBwdDkv, s);
+    varlen_bwd_kernel<T, D, true><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
+  }
   VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
   return 0;
 }

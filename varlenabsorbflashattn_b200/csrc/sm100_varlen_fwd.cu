@@ -21,6 +21,7 @@
 
 #include "sm100_common.cuh"
 #include "sm100_kernels.cuh"
+#include "profile.cuh"
 
 namespace vafa {
 namespace {
@@ -494,8 +495,12 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s) {
 
   const size_t smem = sizeof(FwdSmem<D>) + 1024;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  varlen_fwd_kernel<T, D><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
+  {
+    LaunchScope scope(kKFwd, s);
+    varlen_fwd_kernel<T, D><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
+  }
   VAFA_LAUNCH_CHECK("varlen_fwd_kernel");
+  LaunchScope scope(kKCombine, s);
   varlen_combine_kernel<T, D><<<2 * sms, 256, 0, s>>>(sp.header, sp.combine, p.partial_o, p.partial_lse,
                                                       (T*)a->o, a->lse, a->num_heads);
   VAFA_LAUNCH_CHECK("varlen_combine_kernel");
