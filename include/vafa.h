@@ -87,10 +87,33 @@ typedef struct vafa_varlen_args {
   int32_t* status;      /* device, VAFA_STATUS_WORDS int32, may be NULL */
 } vafa_varlen_args;
 
+/* Bytes of scratch built into the library for vafa_varlen_fwd_noalloc() (below). */
+#define VAFA_NOALLOC_SCRATCH_BYTES (16u << 20)
+
 size_t vafa_varlen_fwd_workspace_bytes(const vafa_varlen_args* a);
 size_t vafa_varlen_bwd_workspace_bytes(const vafa_varlen_args* a);
 int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream);
 int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream);
+
+/* Forward pass for callers that cannot provide a workspace.  No counterpart in the reference:
+ * there, torch's allocator is always at hand.  Some hosts of this library are not in that
+ * position -- a plugin running inside another runtime's execution callback, an inference engine
+ * whose memory plan is frozen before the first request, a real-time loop that may not touch
+ * the allocator -- so they cannot call cudaMalloc (or have torch do it) to size a workspace per
+ * batch.  This entry point takes the same arguments as vafa_varlen_fwd but ignores `workspace`
+ * and `workspace_bytes`: its tile lists and split-K partials live in a fixed
+ * VAFA_NOALLOC_SCRATCH_BYTES array inside the library's device image (each GPU that loads the
+ * library holds that much until the process exits).  It calls no allocation routine of any kind.
+ *   - tcgen05 shapes only (bf16/fp16, head_dim 64 or 128); others return VAFA_ERR_UNSUPPORTED.
+ *   - Batches whose tile lists do not fit return VAFA_ERR_WORKSPACE with the sizes in the error
+ *     text; the split-K partial area shrinks to whatever room is left, so long-KV batches may
+ *     be split less finely than with vafa_varlen_fwd (same result up to fp32 rounding).
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current) and caches it; make that first call outside of any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's
+ *     contents; every call rewrites what it reads, so nothing has to be cleared, but two calls
+ *     that may overlap on the GPU (different streams) race -- serialise them. */
+int vafa_varlen_fwd_noalloc(const vafa_varlen_args* a, vafa_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * Absorbed ragged target attention (u = q_raw W_Q W_K^T per head, attend over raw X,

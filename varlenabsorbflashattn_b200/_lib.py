@@ -24,6 +24,7 @@ DTYPE_CODE = {torch.float32: VAFA_F32, torch.bfloat16: VAFA_BF16, torch.float16:
 EXPORTS = (
     "vafa_abi_version", "vafa_last_error", "vafa_check_status", "vafa_cast_from_f32",
     "vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes", "vafa_varlen_fwd", "vafa_varlen_bwd",
+    "vafa_varlen_fwd_noalloc",
     "vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes",
     "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
     "vafa_profile_enable", "vafa_profile_kernel_count", "vafa_profile_kernel_name", "vafa_profile_read",
@@ -82,7 +83,7 @@ def load() -> C.CDLL:
         for name in ("vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes"):
             getattr(lib, name).argtypes = [C.POINTER(VarlenArgs)]
             getattr(lib, name).restype = C.c_size_t
-        for name in ("vafa_varlen_fwd", "vafa_varlen_bwd"):
+        for name in ("vafa_varlen_fwd", "vafa_varlen_bwd", "vafa_varlen_fwd_noalloc"):
             getattr(lib, name).argtypes = [C.POINTER(VarlenArgs), C.c_void_p]
             getattr(lib, name).restype = C.c_int
         for name in ("vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes"):

@@ -17,6 +17,7 @@
 // P rounded to the I/O dtype before P.V, fp32 row sums from the unrounded P, O = acc / l,
 // LSE = m + log2(l).
 #include <cuda.h>
+#include <mutex>
 #include <type_traits>
 
 #include "sm100_common.cuh"
@@ -445,13 +446,21 @@ struct FwdWorkspace {
   SchedCaps caps;
 };
 
-FwdWorkspace fwd_workspace(const vafa_varlen_args* a, int sm_count) {
+// `limit` > 0 shrinks the split-K partial area so that the whole layout fits in `limit` bytes
+// (the scheduler then splits less, or not at all); total > limit afterwards means it cannot fit.
+FwdWorkspace fwd_workspace(const vafa_varlen_args* a, int sm_count, size_t limit = 0) {
   FwdWorkspace w;
   w.caps = sched_caps(kSchedFwd, a->total_q, a->total_k, a->n_seg, a->num_heads, sm_count, a->split_k_block);
   w.header = 0;
   w.items = 256;
   w.combine = w.items + align_up((size_t)w.caps.cap_items * sizeof(WorkItem), 256);
   w.plse = w.combine + align_up((size_t)w.caps.cap_combine * sizeof(CombineUnit), 256);
+  if (limit > 0) {
+    const size_t per_row = (size_t)a->num_heads * (a->head_dim + 1) * 4;
+    const size_t room = limit > w.plse + 1024 ? limit - w.plse - 1024 : 0;
+    const size_t rows = room / per_row;
+    if (rows < (size_t)w.caps.cap_rows) w.caps.cap_rows = (int32_t)rows;
+  }
   w.po = w.plse + align_up((size_t)w.caps.cap_rows * a->num_heads * 4, 256);
   w.total = w.po + align_up((size_t)w.caps.cap_rows * a->num_heads * a->head_dim * 4, 256);
   return w;
@@ -465,11 +474,13 @@ int resolve_sm_count(int given) {
   return n;
 }
 
+// `scratch` == nullptr: the caller's workspace with the default layout; otherwise the given
+// buffer of `scratch_bytes` with a layout shrunk to fit it.
 template <typename T, int D>
-int launch_fwd(const vafa_varlen_args* a, cudaStream_t s) {
+int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullptr, size_t scratch_bytes = 0) {
   const int sms = resolve_sm_count(a->sm_count);
-  const FwdWorkspace ws = fwd_workspace(a, sms);
-  char* base = (char*)a->workspace;
+  const FwdWorkspace ws = fwd_workspace(a, sms, scratch ? scratch_bytes : 0);
+  char* base = scratch ? (char*)scratch : (char*)a->workspace;
   SchedParams sp;
   sp.cu_q = a->cu_seqlens_q; sp.cu_k = a->cu_seqlens_k; sp.n_seg = a->n_seg; sp.mode = kSchedFwd;
   sp.causal = a->causal; sp.H = a->num_heads; sp.sm_count = sms; sp.split_len = a->split_k_block;
@@ -527,6 +538,59 @@ int sm100_varlen_fwd(const vafa_varlen_args* a, cudaStream_t s) {
     return a->head_dim == 128 ? launch_fwd<__nv_bfloat16, 128>(a, s) : launch_fwd<__nv_bfloat16, 64>(a, s);
   }
   return a->head_dim == 128 ? launch_fwd<__half, 128>(a, s) : launch_fwd<__half, 64>(a, s);
+}
+
+// ---------------- forward without any allocation by anyone ------------------------------------
+// Scratch for vafa_varlen_fwd_noalloc(): a fixed array in the library's own device image.  Every
+// GPU that loads the library carries these bytes until the process exits.
+constexpr size_t kNoAllocScratchBytes = VAFA_NOALLOC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of g_noalloc_scratch on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel can use, so the address is asked for
+// once per device (with that device current) and cached.
+int noalloc_scratch(void** out) {
+  int dev = -1;
+  VAFA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(VAFA_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(VAFA_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace
+
+int sm100_varlen_fwd_noalloc(const vafa_varlen_args* a, cudaStream_t s) {
+  const int sms = resolve_sm_count(a->sm_count);
+  const FwdWorkspace ws = fwd_workspace(a, sms, kNoAllocScratchBytes);
+  if (ws.total > kNoAllocScratchBytes)
+    return fail(VAFA_ERR_WORKSPACE,
+                "vafa_varlen_fwd_noalloc: the tile lists of this batch need %zu bytes, more than the built-in "
+                "%zu-byte scratch (they grow with total_q/128 + n_seg); use vafa_varlen_fwd with a caller-owned "
+                "workspace",
+                ws.total, kNoAllocScratchBytes);
+  void* scratch = nullptr;
+  int rc = noalloc_scratch(&scratch);
+  if (rc) return rc;
+  if (a->dtype == VAFA_BF16) {
+    return a->head_dim == 128 ? launch_fwd<__nv_bfloat16, 128>(a, s, scratch, kNoAllocScratchBytes)
+                              : launch_fwd<__nv_bfloat16, 64>(a, s, scratch, kNoAllocScratchBytes);
+  }
+  return a->head_dim == 128 ? launch_fwd<__half, 128>(a, s, scratch, kNoAllocScratchBytes)
+                            : launch_fwd<__half, 64>(a, s, scratch, kNoAllocScratchBytes);
 }
 
 }  // namespace vafa

@@ -253,6 +253,14 @@ int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream) {
   return simt_attn_fwd(simt_from_varlen(a), s);
 }
 
+int vafa_varlen_fwd_noalloc(const vafa_varlen_args* a, vafa_stream_t stream) {
+  int rc = check_varlen(a, false);
+  if (rc) return rc;
+  if (!varlen_fwd_tc_ok(a))
+    return fail(VAFA_ERR_UNSUPPORTED, "vafa_varlen_fwd_noalloc covers bf16/fp16 with head_dim 64 or 128 only");
+  return sm100_varlen_fwd_noalloc(a, (cudaStream_t)stream);
+}
+
 int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream) {
   int rc = check_varlen(a, true);
   if (rc) return rc;
