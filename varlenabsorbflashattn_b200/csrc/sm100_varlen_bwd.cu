@@ -33,12 +33,13 @@ namespace {
 
 using namespace ptx;
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
+constexpr int kLdRow = 68;        // float2 slots per staged (lse, delta) block: 64 + 2 of alignment slack, padded
 constexpr int kInner = 64;  // rows per inner block
 
 template <int D>
 struct BwdCfg {
-  static constexpr int kStages = (D == 128) ? 3 : 4;
+  static constexpr int kStages = (D == 128) ? 4 : 8;
   static constexpr int kSub = D / 64;
   static constexpr int kOuterSubBytes = 128 * 128;   // 128 rows x 128 B
   static constexpr int kInnerSubBytes = kInner * 128;  // 64 rows x 128 B
@@ -57,9 +58,12 @@ struct BwdSmem {
   alignas(8) uint64_t outer_full, outer_free;
   uint64_t in_full[BwdCfg<D>::kStages], in_empty[BwdCfg<D>::kStages];
   uint64_t xy_full[2], ds_full[2], acc_done;
+  alignas(16) float2 ld[BwdCfg<D>::kStages][kLdRow];  // dKV: (lse, delta) of the inner block's query rows
   uint32_t tmem_base;
   int abort_flag;
 };
+
+static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
 
 struct BwdParams {
   void* out0;            // dQ, or dV
@@ -96,18 +100,18 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.xy_full[i]), 1);
-      mbar_init(smem_u32(&sm.ds_full[i]), 128);
+      mbar_init(smem_u32(&sm.ds_full[i]), 256);
     }
     mbar_init(smem_u32(&sm.acc_done), 1);
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     prefetch_tensormap(&tmap_outer_a);
     prefetch_tensormap(&tmap_outer_b);
     prefetch_tensormap(&tmap_inner_a);
     prefetch_tensormap(&tmap_inner_b);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&sm.tmem_base), Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -121,7 +125,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   const int G = gridDim.x, cta = blockIdx.x;
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, kDKV ? 120 : 110, n_items);
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
@@ -144,7 +148,13 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * kInner;
           if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
-          mbar_expect_tx(smem_u32(&sm.in_full[st]), 2 * Cfg::kInnerBytes);
+          mbar_expect_tx(smem_u32(&sm.in_full[st]), 2 * Cfg::kInnerBytes + (kDKV ? 66 * 8 : 0));
+          if (kDKV) {
+            // (lse, delta) pairs of rows [row, row+64): the copy starts at the even index below `row`
+            // (16-byte alignment) and takes 66 pairs; readers skip (row & 1) slots
+            const float2* src = p.ld + (long long)h * p.ld_stride + (row & ~1);
+            bulk_load_1d(smem_u32(&sm.ld[st][0]), src, 66 * 8, smem_u32(&sm.in_full[st]));
+          }
           for (int c = 0; c < Cfg::kSub; ++c) {
             tma_load_3d(smem_u32(sm.inner_a[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_a, smem_u32(&sm.in_full[st]), c * 64, h, row);
             tma_load_3d(smem_u32(sm.inner_b[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_b, smem_u32(&sm.in_full[st]), c * 64, h, row);
@@ -153,7 +163,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         ++qi;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -212,19 +222,19 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             // dQ += dS . K_g     (dS in X, 16-bit packed; K block MN-major)
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc0, x_tmem + kk * 8,
+              mma_ts(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
                      make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
                      (acc | (kk > 0)) ? 1u : 0u);
           } else {
             // dV += P^T . dO_g ;  dK += dS^T . Q_g
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc0, x_tmem + kk * 8,
+              mma_ts(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
                      make_desc_sw128(smem_u32(sm.inner_b[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
                      (acc | (kk > 0)) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc1, y_tmem + kk * 8,
+              mma_ts(tbase + Cfg::kAcc1, y_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
                      make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
                      (acc | (kk > 0)) ? 1u : 0u);
           }
@@ -236,9 +246,12 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       }
     }
   } else {
-    // ---------------- element-wise warps + epilogue (warps 0-3) ----------------
-    const int r = threadIdx.x;
-    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+    // ---------------- element-wise warps + epilogue (warps 0-7) ----------------
+    // thread -> outer row r = tid % 128 (TMEM lane; a warp may only touch lane quadrant warp % 4);
+    // warps 0-3 take inner columns [0,32) of every block, warps 4-7 columns [32,64)
+    const int r = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
+    const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     const float c = p.scale_log2;
     uint32_t gk = 0, qi = 0;
     bool alive = true;
@@ -275,8 +288,14 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           else lo = r + w.diag - b * kInner;
         }
         const bool need_mask = (hi < kInner - 1) || (lo > 0);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        const int st = g % S;
+        const int ld_skip = (w.i_start + b * kInner) & 1;
+        if (kDKV) {
+          // the staged (lse, delta) block arrived with this stage's tiles (already complete here;
+          // this wait only orders the reads below after the copy)
+          if (!mbar_wait(smem_u32(&sm.in_full[st]), (g / S) & 1, abort_flag)) { alive = false; break; }
+        }
+        {
           uint32_t xs[32], ys[32];
           tmem_ld32(x_addr + half * 32, xs);
           tmem_ld32(y_addr + half * 32, ys);
@@ -290,7 +309,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
               const int col = half * 32 + i + e;
               float lse_v, delta_v;
               if (kDKV) {
-                const float2 t = __ldg(&ld_h[w.i_start + b * kInner + col]);
+                const float2 t = sm.ld[st][ld_skip + col];
                 lse_v = t.x;
                 delta_v = t.y;
               } else {
@@ -310,12 +329,14 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             pp[i >> 1] = pack2<T>(pv[0], pv[1]);
             dd[i >> 1] = pack2<T>(dv[0], dv[1]);
           }
-          // 32 fp32 columns become 16 packed columns: half h lands at packed columns [16h, 16h+16)
+          // 32 fp32 columns become 16 packed columns, written over the first 16 of the columns this
+          // thread has just read, so the two halves never touch each other's source columns; the MMA
+          // issuer addresses K-step kk at column (kk/2)*32 + (kk%2)*8
           if (!kDKV) {
-            tmem_st16(x_addr + half * 16, dd);
+            tmem_st16(x_addr + half * 32, dd);
           } else {
-            tmem_st16(x_addr + half * 16, pp);
-            tmem_st16(y_addr + half * 16, dd);
+            tmem_st16(x_addr + half * 32, pp);
+            tmem_st16(y_addr + half * 32, dd);
           }
         }
         tmem_wait_st();
@@ -338,7 +359,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         const float mul = (kDKV && which == 0) ? 1.f : p.scale;  // dV unscaled; dQ and dK scaled
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int c2 = 0; c2 < D / 64; ++c2) {
+          const int cc = half * (D / 64) + c2;  // each half of the compute warps writes half of the columns
           uint32_t t[32];
           if (nb > 0) {
             tmem_ld32(lane_base + acc_col + cc * 32, t);

@@ -29,12 +29,22 @@ namespace {
 
 using namespace ptx;
 
+// Optional wait-time tracing (build with -DVAFA_TRACE): per CTA, cycles each role spent waiting on
+// each barrier, written to FwdParams::trace[cta][16].
+#ifdef VAFA_TRACE
+#define TRACE_T0() const long long _t0 = clock64()
+#define TRACE_ADD(slot) tr[slot] += clock64() - _t0
+#else
+#define TRACE_T0()
+#define TRACE_ADD(slot)
+#endif
+
 constexpr int kFwdThreads = 192;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  static constexpr int kStages = (D == 128) ? 3 : 6;
   static constexpr int kSub = D / 64;                 // 64-column (128-byte) sub tiles per row
   static constexpr int kSubBytes = 128 * 128;         // one sub tile: 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;
@@ -55,6 +65,8 @@ struct FwdSmem {
   int abort_flag;
 };
 
+static_assert(sizeof(FwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(FwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
+
 struct FwdParams {
   void* o;
   float* lse;
@@ -65,6 +77,7 @@ struct FwdParams {
   int H;
   float scale_log2;
   int32_t* status;
+  long long* trace;
 };
 
 template <typename T, int D>
@@ -113,6 +126,11 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const long long total = (long long)max(n_items, 0) * p.H;
   const int G = gridDim.x, cta = blockIdx.x;
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, 100, n_items);
+#ifdef VAFA_TRACE
+  long long tr[16];
+  for (int i = 0; i < 16; ++i) tr[i] = 0;
+  const long long t_begin = clock64();
+#endif
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -126,7 +144,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const int h = (int)(idx % p.H);
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
-        if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
         mbar_expect_tx(smem_u32(&sm.q_full), Cfg::kTileBytes);
         for (int c = 0; c < Cfg::kSub; ++c)
           tma_load_3d(smem_u32(sm.q) + c * Cfg::kSubBytes, &tmap_q, smem_u32(&sm.q_full), c * 64, h, w.o_start);
@@ -134,11 +152,11 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * kTile;
-          if (!mbar_wait(smem_u32(&sm.k_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.k_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
             tma_load_3d(smem_u32(sm.k[st]) + c * Cfg::kSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
-          if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
           mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
             tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
@@ -158,7 +176,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       auto issue_qk = [&](uint32_t g, bool last) -> bool {
         const int st = g % S;
         const uint32_t ph = (g / S) & 1;
-        if (!mbar_wait(smem_u32(&sm.k_full[st]), ph, abort_flag)) return false;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.k_full[st]), ph, abort_flag)) return false; TRACE_ADD(4); }
         tc_fence_after();
         const uint32_t d_tmem = tbase + (g & 1) * 128;
 #pragma unroll
@@ -180,7 +198,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const WorkItem w = p.items[idx / p.H];
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
-        if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
         tc_fence_after();
         if (!issue_qk(gk, nb == 1)) break;
         for (int b = 0; b < nb; ++b) {
@@ -190,8 +208,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           }
           const int st = g % S;
           const uint32_t ph = (g / S) & 1;
-          if (!mbar_wait(smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
-          if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(5); }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
           tc_fence_after();
           const uint32_t a_tmem = tbase + (g & 1) * 128;
 #pragma unroll
@@ -225,8 +243,11 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
       for (int b = 0; b < nb; ++b) {
         const uint32_t g = gk + b;
-        if (!mbar_wait(smem_u32(&sm.s_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.s_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(8); }
         tc_fence_after();
+#ifdef VAFA_TRACE
+        const long long t_sm0 = clock64();
+#endif
         const uint32_t s_addr = lane_base + (g & 1) * 128;
         float s[128];
         {
@@ -252,25 +273,35 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
           for (int i = 0; i < 128; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
         }
-        float mx = s[0];
+        // row maximum: eight independent chains of 3-input max (one warp per scheduler has no
+        // other warp to hide a serial chain's latency behind)
+        float m8[8];
 #pragma unroll
-        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        for (int j = 0; j < 8; ++j) m8[j] = max3(s[j], s[8 + j], s[16 + j]);
+#pragma unroll
+        for (int i = 24; i < 120; i += 16) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) m8[j] = max3(m8[j], s[i + j], s[i + 8 + j]);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m8[j] = fmaxf(m8[j], s[120 + j]);
+        const float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
         const float m_blk = mx * c;  // c > 0
         float m_new = fmaxf(m_ref, m_blk);
         const bool resc = m_new > m_ref + kRescaleThreshold;
         if (!resc) m_new = m_ref;
         const float alpha = resc ? ex2(m_ref - m_new) : 1.f;
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        float sum = 0.f;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t pk[64];
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float p0 = ex2(fmaf(s[2 * i], c, -m_use));
           const float p1 = ex2(fmaf(s[2 * i + 1], c, -m_use));
-          sum += p0 + p1;
+          sum4[i & 3] += p0 + p1;
           pk[i] = pack2<T>(p0, p1);
         }
-        l = l * alpha + sum;
+        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_ref = m_new;
         {
           uint32_t a0[32], a1[32];
@@ -280,9 +311,15 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           tmem_st32(s_addr + 32, a1);
         }
         if (b > 0) {
-          if (!mbar_wait(smem_u32(&sm.o_done), (g - 1) & 1, abort_flag)) { alive = false; break; }
+#ifdef VAFA_TRACE
+          tr[10] += clock64() - t_sm0;
+#endif
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done), (g - 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
           tc_fence_after();
           if (__any_sync(0xffffffffu, resc)) {
+#ifdef VAFA_TRACE
+            tr[12] += 1;
+#endif
 #pragma unroll
             for (int cc = 0; cc < D / 32; ++cc) {
               uint32_t t[32];
@@ -297,9 +334,15 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.p_full[g & 1]));
+#ifdef VAFA_TRACE
+        tr[11] += 1;
+#endif
       }
       if (!alive) break;
       gk += nb;
+#ifdef VAFA_TRACE
+      const long long t_ep0 = clock64();
+#endif
 
       // ---- epilogue ----
       if (nb > 0) {
@@ -364,6 +407,10 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         if (row_ok) p.partial_lse[prow * p.H + h] = lse_val;
       }
+#ifdef VAFA_TRACE
+      tr[13] += clock64() - t_ep0;
+      tr[14] += 1;
+#endif
       // the TMEM reads of O above must finish before the next item's first P.V overwrites O;
       // that MMA is issued only after this thread's next p_full arrival, which follows in
       // program order (tcgen05.wait::ld has completed every read).
@@ -371,6 +418,13 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   }
 
   // ---------------- teardown ----------------
+#ifdef VAFA_TRACE
+  if (p.trace != nullptr && (threadIdx.x == 0 || threadIdx.x == 128 || threadIdx.x == 160)) {
+    tr[15] = clock64() - t_begin;
+    for (int i = 0; i < 16; ++i)
+      if (tr[i] != 0) p.trace[(long long)blockIdx.x * 16 + i] = tr[i];
+  }
+#endif
   tc_fence_before();
   __syncthreads();
   if (sm.abort_flag != 0) {
@@ -441,6 +495,12 @@ __global__ void __launch_bounds__(256) varlen_combine_kernel(const SchedHeader* 
   }
 }
 
+#ifdef VAFA_TRACE
+}  // namespace
+long long* vafa_trace_buffer = nullptr;
+namespace {
+#endif
+
 struct FwdWorkspace {
   size_t header, items, combine, plse, po, total;
   SchedCaps caps;
@@ -503,6 +563,16 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   p.header = sp.header; p.items = sp.items; p.H = a->num_heads;
   p.scale_log2 = a->scale * kLog2e;
   p.status = a->status;
+  p.trace = nullptr;
+#ifdef VAFA_TRACE
+  {
+    static long long* g_trace = nullptr;  // debugging aid only: leaked on purpose
+    if (!g_trace) cudaMalloc(&g_trace, 1024 * 16 * sizeof(long long));
+    cudaMemsetAsync(g_trace, 0, 1024 * 16 * sizeof(long long), s);
+    p.trace = g_trace;
+    vafa_trace_buffer = g_trace;
+  }
+#endif
 
   const size_t smem = sizeof(FwdSmem<D>) + 1024;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -594,3 +664,10 @@ int sm100_varlen_fwd_noalloc(const vafa_varlen_args* a, cudaStream_t s) {
 }
 
 }  // namespace vafa
+
+#ifdef VAFA_TRACE
+extern "C" __attribute__((visibility("default"))) int vafa_trace_read(long long* host, int n_ctas) {
+  if (!vafa::vafa_trace_buffer) return -1;
+  return (int)cudaMemcpy(host, vafa::vafa_trace_buffer, (size_t)n_ctas * 16 * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+#endif
