@@ -194,6 +194,8 @@ class _TargetAttnInner(torch.autograd.Function):
             a.o, a.lse = O.data_ptr(), lse.data_ptr()
             saved = torch.empty(max(1, lib.vafa_absorb_saved_bytes(a)), dtype=torch.uint8, device=dev)
             a.saved = saved.data_ptr()
+            ws = _lib.workspace(lib.vafa_absorb_fwd_workspace_bytes(a), dev)
+            a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_absorb_inner_fwd(a, _stream()), "vafa_absorb_inner_fwd")
         ctx.save_for_backward(u, X, W_V, O, lse, cu_q, cu_k, saved)
         ctx.scale = scale

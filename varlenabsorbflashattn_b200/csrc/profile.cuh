@@ -20,6 +20,7 @@ enum KernelId {
   kKCast,
   kKAbsorbFwd,
   kKAbsorbBwd,
+  kKAbsorbGemm,
   kKCount
 };
 

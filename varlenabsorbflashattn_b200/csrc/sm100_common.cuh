@@ -9,9 +9,11 @@
 namespace vafa {
 
 // Encode a tiled, 128-byte-swizzled tensor map over a row-major [rows, heads, dim] tensor of
-// 16-bit elements (heads = 1, dim = row width for a plain matrix).  Box = 64 columns x 1 head x
-// box_rows rows, so one copy fills one [box_rows x 128 B] swizzled sub-tile.
-int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows, int heads, int dim, int box_rows);
+// 16-bit elements (heads = 1, dim = row width for a plain matrix).  Box = 64 columns x box_heads heads x
+// box_rows rows, so one copy fills one [(box_rows * box_heads) x 128 B] swizzled sub-tile (row-major
+// over (row, head)).
+int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows, int heads, int dim, int box_rows,
+                     int box_heads = 1);
 
 // Persistent CTAs walk the cost-sorted item list in "snake" order: pass n covers items
 // [n*G, (n+1)*G), forwards on even passes and backwards on odd ones, so that the CTA that drew

@@ -15,4 +15,34 @@ int sm100_varlen_bwd(const vafa_varlen_args* a, cudaStream_t s);
 // forward with the library's built-in scratch array instead of a workspace
 int sm100_varlen_fwd_noalloc(const vafa_varlen_args* a, cudaStream_t s);
 
+// ---- absorb operator on the tcgen05 kernels ------------------------------------------------
+// Attention core on a pre-projected u: axn[t,h,:] = softmax_h(scale * u[t,h,:] . X^T) . X, normalised,
+// in the I/O dtype; lse[t,h] log2-domain.  Requires d_kv == 256, 16-bit dtype, H dividing 128.
+struct AbsorbCoreArgs {
+  const void* u;       // [T_q, H, 256]
+  const void* x;       // [T_k, 256]
+  void* axn;           // [T_q, H, 256]
+  float* lse;          // [T_q, H]
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int n_seg, total_q, total_k, H, dtype;
+  float scale;
+  int sm_count;
+  void* workspace;
+  int32_t* status;
+};
+size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H);
+int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s);
+
+// C[M, ldc] (16-bit) = A[M, 256] . B[256, N] with A rows K-major (row stride lda elements) and B
+// row-major [256, N] (N a multiple of 256, row stride ldb).  diag_heads > 0: row m keeps only the
+// 256/diag_heads columns of block (m % diag_heads) and writes them to C[m, 0 : 256/diag_heads]
+// (per-head projection of head-stacked rows); N must then be 256.
+struct GemmNNArgs {
+  const void* A; const void* B; void* C;
+  long long M; int N; int lda, ldb, ldc;
+  int dtype; int diag_heads; int sm_count;
+};
+int sm100_gemm_nn_k256(const GemmNNArgs& g, cudaStream_t s);
+
 }  // namespace vafa

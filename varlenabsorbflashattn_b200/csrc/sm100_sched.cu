@@ -33,10 +33,10 @@ __device__ __forceinline__ void for_each_unit(const SchedParams& p, F f) {
         f(u);
       }
     } else {
-      for (int i0 = 0; i0 < Lq; i0 += kTile) {
+      for (int i0 = 0; i0 < Lq; i0 += p.tile_rows) {
         Unit u;
         u.o_start = q0 + i0;
-        u.o_rows = min(kTile, Lq - i0);
+        u.o_rows = min(p.tile_rows, Lq - i0);
         int kend = Lk;
         if (p.causal) kend = min(Lk, i0 + u.o_rows + off);
         u.i_len = max(0, kend);

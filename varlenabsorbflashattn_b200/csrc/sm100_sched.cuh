@@ -56,6 +56,7 @@ struct SchedParams {
   int32_t H;
   int32_t sm_count;
   int32_t split_len;    // forced inner slice length (multiple of 128), 0 = automatic
+  int32_t tile_rows = kTile;  // outer rows per tile in the forward / dQ modes (absorb: 128 / H)
   int32_t cap_items;
   int32_t cap_combine;
   int32_t cap_rows;

@@ -28,15 +28,17 @@ EncodeTiledFn get_encode() {
 
 }  // namespace
 
-int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows, int heads, int dim, int box_rows) {
+int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows, int heads, int dim, int box_rows,
+                     int box_heads) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return fail(VAFA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if (dtype != VAFA_BF16 && dtype != VAFA_F16) return fail(VAFA_ERR_UNSUPPORTED, "tensor maps are built for 16-bit types only");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(VAFA_ERR_INVALID, "tensor base must be 16-byte aligned");
-  if (dim % 64 != 0 || box_rows < 1 || box_rows > 256) return fail(VAFA_ERR_INVALID, "bad tensor map shape");
+  if (dim % 64 != 0 || box_rows < 1 || box_rows > 256 || box_heads < 1 || box_heads > heads || box_heads * box_rows > 256)
+    return fail(VAFA_ERR_INVALID, "bad tensor map shape");
   cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
   cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)heads * dim * 2};
-  cuuint32_t box[3] = {64, 1, (cuuint32_t)box_rows};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_heads, (cuuint32_t)box_rows};
   cuuint32_t es[3] = {1, 1, 1};
   const CUtensorMapDataType dt = dtype == VAFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   const CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,

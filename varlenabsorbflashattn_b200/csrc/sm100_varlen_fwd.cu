@@ -44,7 +44,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = (D == 128) ? 3 : 6;
+  static constexpr int kStages = (D == 128) ? 3 : (D == 64 ? 6 : 2);
   static constexpr int kSub = D / 64;                 // 64-column (128-byte) sub tiles per row
   static constexpr int kSubBytes = 128 * 128;         // one sub tile: 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;
@@ -52,11 +52,13 @@ struct FwdCfg {
   static constexpr uint32_t kOCol = 256;
 };
 
-template <int D>
+// kAbsorb: keys and values are the same rows (the absorb operator attends over raw X), so there
+// is one ring and no V tiles.
+template <int D, bool kAbsorb = false>
 struct FwdSmem {
   alignas(1024) uint8_t q[FwdCfg<D>::kTileBytes];
   alignas(1024) uint8_t k[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
-  alignas(1024) uint8_t v[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t v[kAbsorb ? 1 : FwdCfg<D>::kStages][kAbsorb ? 1024 : FwdCfg<D>::kTileBytes];
   alignas(8) uint64_t q_full, q_free;
   uint64_t k_full[FwdCfg<D>::kStages], k_empty[FwdCfg<D>::kStages];
   uint64_t v_full[FwdCfg<D>::kStages], v_empty[FwdCfg<D>::kStages];
@@ -65,7 +67,9 @@ struct FwdSmem {
   int abort_flag;
 };
 
-static_assert(sizeof(FwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(FwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
+static_assert(sizeof(FwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(FwdSmem<64>) + 1024 <= 227 * 1024 &&
+                  sizeof(FwdSmem<256, true>) + 1024 <= 227 * 1024,
+              "shared memory budget");
 
 struct FwdParams {
   void* o;
@@ -80,14 +84,19 @@ struct FwdParams {
   long long* trace;
 };
 
-template <typename T, int D>
+// kAbsorb = false: one item = one 128-row query tile of one head (grid of items x heads).
+// kAbsorb = true : one item = 128/H query rows of one user with all H heads stacked into the 128
+//   tile rows (row = q*H + h, the order the 64 x H x (128/H) TMA box delivers), K = V = the user's X
+//   rows (one tile serves Q.X^T as a K-major operand and P.X as an MN-major operand), D = d_kv.
+template <typename T, int D, bool kAbsorb>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
-  FwdSmem<D>& sm = *reinterpret_cast<FwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using Smem = FwdSmem<D, kAbsorb>;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -123,7 +132,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tbase = sm.tmem_base;
 
   const int n_items = p.header->n_items;
-  const long long total = (long long)max(n_items, 0) * p.H;
+  const int HW = kAbsorb ? 1 : p.H;  // work units per item
+  const long long total = (long long)max(n_items, 0) * HW;
   const int G = gridDim.x, cta = blockIdx.x;
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, 100, n_items);
 #ifdef VAFA_TRACE
@@ -140,8 +150,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
         const long long idx = snake_index(pass, cta, G);
         if (idx >= total) continue;
-        const WorkItem w = p.items[idx / p.H];
-        const int h = (int)(idx % p.H);
+        const WorkItem w = p.items[idx / HW];
+        const int h = (int)(idx % HW);
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
@@ -156,10 +166,12 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
             tma_load_3d(smem_u32(sm.k[st]) + c * Cfg::kSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
-          mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
-          for (int c = 0; c < Cfg::kSub; ++c)
-            tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
+          if (!kAbsorb) {
+            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
+            mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
+            for (int c = 0; c < Cfg::kSub; ++c)
+              tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
+          }
         }
         ++qi;
       }
@@ -186,7 +198,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const uint64_t db = make_desc_sw128(smem_u32(sm.k[st]) + off, 16, 1024);
           mma_ss(d_tmem, da, db, idesc_qk, kk > 0);
         }
-        mma_commit(smem_u32(&sm.k_empty[st]));
+        if (!kAbsorb) mma_commit(smem_u32(&sm.k_empty[st]));  // absorb: the tile is still needed for P.X
         mma_commit(smem_u32(&sm.s_full[g & 1]));
         if (last) mma_commit(smem_u32(&sm.q_free));
         return true;
@@ -195,7 +207,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
         const long long idx = snake_index(pass, cta, G);
         if (idx >= total) continue;
-        const WorkItem w = p.items[idx / p.H];
+        const WorkItem w = p.items[idx / HW];
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
@@ -209,16 +221,16 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int st = g % S;
           const uint32_t ph = (g / S) & 1;
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(5); }
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
+          if (!kAbsorb) { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
           tc_fence_after();
           const uint32_t a_tmem = tbase + (g & 1) * 128;
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk) {
             // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart
-            const uint64_t db = make_desc_sw128(smem_u32(sm.v[st]) + kk * 2048, Cfg::kSubBytes, 1024);
+            const uint64_t db = make_desc_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]) + kk * 2048, Cfg::kSubBytes, 1024);
             mma_ts(tbase + Cfg::kOCol, a_tmem + kk * 8, db, idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
           }
-          mma_commit(smem_u32(&sm.v_empty[st]));
+          mma_commit(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.v_empty[st]));
           mma_commit(smem_u32(&sm.o_done));
         }
         gk += nb;
@@ -235,10 +247,12 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
       const long long idx = snake_index(pass, cta, G);
       if (idx >= total) continue;
-      const WorkItem w = p.items[idx / p.H];
-      const int h = (int)(idx % p.H);
+      const WorkItem w = p.items[idx / HW];
       const int nb = (w.i_len + kTile - 1) / kTile;
-      const bool row_ok = r < w.o_rows;
+      // tile row r -> (query row of the tile, head)
+      const int rq = kAbsorb ? r / p.H : r;
+      const int h = kAbsorb ? r % p.H : (int)(idx % HW);
+      const bool row_ok = rq < w.o_rows;
       float m_ref = -INFINITY, l = 0.f;
 
       for (int b = 0; b < nb; ++b) {
@@ -353,7 +367,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const float inv_l = dead ? 0.f : 1.f / l;
       const float lse_val = dead ? -INFINITY : m_ref + log2f(l);
       if (w.partial < 0) {
-        const long long row = (long long)w.o_start + r;
+        const long long row = (long long)w.o_start + rq;
         T* optr = reinterpret_cast<T*>(p.o) + (row * p.H + h) * D;
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
@@ -380,7 +394,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         if (row_ok) p.lse[row * p.H + h] = lse_val;
       } else {
-        const long long prow = (long long)w.partial + r;
+        const long long prow = (long long)w.partial + rq;
         float* optr = p.partial_o + (prow * p.H + h) * D;
 #pragma unroll
         for (int cc = 0; cc < D / 32; ++cc) {
@@ -574,11 +588,11 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   }
 #endif
 
-  const size_t smem = sizeof(FwdSmem<D>) + 1024;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const size_t smem = sizeof(FwdSmem<D, false>) + 1024;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     LaunchScope scope(kKFwd, s);
-    varlen_fwd_kernel<T, D><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
+    varlen_fwd_kernel<T, D, false><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
   }
   VAFA_LAUNCH_CHECK("varlen_fwd_kernel");
   LaunchScope scope(kKCombine, s);
@@ -588,7 +602,62 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   return 0;
 }
 
+struct AbsorbCoreWs {
+  size_t header, items, total;
+  SchedCaps caps;
+};
+
+AbsorbCoreWs absorb_core_ws(int total_q, int n_seg, int H) {
+  AbsorbCoreWs w;
+  const int tile_rows = kTile / H;
+  w.caps.cap_items = total_q / tile_rows + n_seg + 1;
+  w.caps.cap_combine = 0;
+  w.caps.cap_rows = 0;
+  w.header = 0;
+  w.items = 256;
+  w.total = w.items + align_up((size_t)w.caps.cap_items * sizeof(WorkItem), 256);
+  return w;
+}
+
+template <typename T>
+int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
+  constexpr int D = 256;
+  const int sms = resolve_sm_count(a.sm_count);
+  const AbsorbCoreWs ws = absorb_core_ws(a.total_q, a.n_seg, a.H);
+  char* base = (char*)a.workspace;
+  SchedParams sp;
+  sp.cu_q = a.cu_q; sp.cu_k = a.cu_k; sp.n_seg = a.n_seg; sp.mode = kSchedDq;  // no split-K
+  sp.causal = 0; sp.H = 1; sp.sm_count = sms; sp.split_len = 0; sp.tile_rows = kTile / a.H;
+  sp.cap_items = ws.caps.cap_items; sp.cap_combine = 0; sp.cap_rows = 0;
+  sp.header = (SchedHeader*)(base + ws.header);
+  sp.items = (WorkItem*)(base + ws.items);
+  sp.combine = nullptr;
+  int rc = launch_scheduler(sp, s);
+  if (rc) return rc;
+  CUtensorMap tu, tx;
+  if ((rc = encode_tmap_rows(&tu, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
+  if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, D, 128))) return rc;
+  FwdParams p;
+  p.o = a.axn; p.lse = a.lse; p.partial_o = nullptr; p.partial_lse = nullptr;
+  p.header = sp.header; p.items = sp.items; p.H = a.H;
+  p.scale_log2 = a.scale * kLog2e;
+  p.status = a.status;
+  p.trace = nullptr;
+  const size_t smem = sizeof(FwdSmem<D, true>) + 1024;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  LaunchScope scope(kKAbsorbFwd, s);
+  varlen_fwd_kernel<T, D, true><<<sms, kFwdThreads, smem, s>>>(tu, tx, tx, p);
+  VAFA_LAUNCH_CHECK("varlen_fwd_kernel<absorb>");
+  return 0;
+}
+
 }  // namespace
+
+size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H) { return absorb_core_ws(total_q, n_seg, H).total; }
+
+int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
+  return a.dtype == VAFA_BF16 ? launch_absorb_core_fwd<__nv_bfloat16>(a, s) : launch_absorb_core_fwd<__half>(a, s);
+}
 
 bool sm100_varlen_fwd_supported(const vafa_varlen_args* a) {
   if (!(a->dtype == VAFA_BF16 || a->dtype == VAFA_F16)) return false;

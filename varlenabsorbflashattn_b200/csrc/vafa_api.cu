@@ -140,9 +140,38 @@ SimtAttnParams simt_from_absorb(const vafa_absorb_args* a, const void* u, void* 
   return p;
 }
 
+// Which parts of the absorb forward run on the tcgen05 kernels.
+struct AbsorbFast {
+  bool core;      // attention over X: 16-bit, d_kv == 256, H divides 128
+  bool prologue;  // u = q_raw (W_Q W_K^T): core && d_q == 256
+  bool epilogue;  // O = axn W_V per head: core && H * D_H == 256 && D_H >= 32
+};
+
+AbsorbFast absorb_fast(const vafa_absorb_args* a, bool inner) {
+  AbsorbFast f{false, false, false};
+  if (a->impl == VAFA_IMPL_SIMT) return f;
+  const int H = a->num_heads;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  f.core = (a->dtype == VAFA_BF16 || a->dtype == VAFA_F16) && a->d_kv == 256 && H >= 1 && H <= 128 && (128 % H) == 0 &&
+           a->total_q > 0 && a->total_k > 0 && a->scale > 0.f && al(a->q_raw) && al(a->x) && al(a->o) && al(a->saved);
+  f.prologue = f.core && !inner && a->d_q == 256 && al(a->w_q) && al(a->w_k);
+  f.epilogue = f.core && H * a->head_dim == 256 && a->head_dim >= 32 && al(a->w_v);
+  return f;
+}
+
+size_t absorb_fwd_ws_bytes(const vafa_absorb_args* a, bool inner) {
+  const AbsorbFast f = absorb_fast(a, inner);
+  size_t n = 0;
+  if (f.prologue) n += align_up((size_t)a->d_q * a->num_heads * a->d_kv * elem_size(a->dtype), 256);
+  if (f.core) n += sm100_absorb_core_fwd_workspace_bytes(a->total_q, a->n_seg, a->num_heads);
+  return n;
+}
+
 int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   const AbsorbSizes z = absorb_sizes(a);
+  const AbsorbFast fast = absorb_fast(a, inner);
   char* sv = (char*)a->saved;
+  char* ws = (char*)a->workspace;
   const int H = a->num_heads, dh = a->head_dim, dkv = a->d_kv, Tq = a->total_q;
   const void* u;
   void* axn;
@@ -150,6 +179,18 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   if (inner) {
     u = a->q_raw;
     axn = sv;
+  } else if (fast.prologue) {
+    // W_QK[a, h, kv] = sum_dd W_Q[a,h,dd] W_K[kv,h,dd]  (tiny), then u = q_raw . W_QK as one product
+    void* wqk = ws;
+    ws += align_up((size_t)a->d_q * H * dkv * elem_size(a->dtype), 256);
+    SimtGemm gw{a->w_q, a->w_k, wqk, a->dtype, a->dtype, a->dtype, a->d_q, dkv, dh, H,
+                (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
+    if ((rc = simt_gemm(gw, s))) return rc;
+    void* ub = sv + z.p;
+    axn = sv + z.p + z.u;
+    GemmNNArgs g{a->q_raw, wqk, ub, Tq, H * dkv, a->d_q, H * dkv, H * dkv, a->dtype, 0, a->sm_count};
+    if ((rc = sm100_gemm_nn_k256(g, s))) return rc;
+    u = ub;
   } else {
     void* p = sv;
     void* ub = sv + z.p;
@@ -164,8 +205,19 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     if ((rc = simt_gemm(g2, s))) return rc;
     u = ub;
   }
-  SimtAttnParams p = simt_from_absorb(a, u, axn);
-  if ((rc = simt_attn_fwd(p, s))) return rc;
+  if (fast.core) {
+    AbsorbCoreArgs c{u, a->x, axn, a->lse, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H, a->dtype,
+                     a->scale, a->sm_count, ws, a->status};
+    if ((rc = sm100_absorb_core_fwd(c, s))) return rc;
+  } else {
+    SimtAttnParams p = simt_from_absorb(a, u, axn);
+    if ((rc = simt_attn_fwd(p, s))) return rc;
+  }
+  if (fast.epilogue) {
+    // rows (t, h) of axn against all of W_V, keeping for each row the D_H columns of its own head
+    GemmNNArgs g{axn, a->w_v, a->o, (long long)Tq * H, H * dh, dkv, H * dh, dh, a->dtype, H, a->sm_count};
+    return sm100_gemm_nn_k256(g, s);
+  }
   // O_h = axn_h W_V_h                    [T_q, H, D_H]; batch over heads
   SimtGemm g3{axn, a->w_v, a->o, a->dtype, a->dtype, a->dtype, Tq, dh, dkv, H,
               (int64_t)H * dkv, 1, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
@@ -188,6 +240,12 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   float* dWK = inner ? nullptr : a->dw + (size_t)dq * H * dh;
   float* dWV = inner ? a->dw : a->dw + (size_t)(dq + dkv) * H * dh;
   int rc;
+  if (!inner && absorb_fast(a, false).prologue) {
+    // the tcgen05 prologue goes straight to u; the weight-gradient chain below needs p = q_raw W_Q
+    SimtGemm gp{a->q_raw, a->w_q, sv, a->dtype, a->dtype, a->dtype, Tq, H * dh, dq, 1,
+                dq, 1, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
+    if ((rc = simt_gemm(gp, s))) return rc;
+  }
   // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
   SimtGemm g1{a->d_o, a->w_v, dax, a->dtype, a->dtype, VAFA_F32, Tq, dkv, dh, H,
               (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
@@ -283,8 +341,8 @@ size_t vafa_absorb_saved_bytes(const vafa_absorb_args* a) {
   return z.p + z.u + z.axn;
 }
 size_t vafa_absorb_fwd_workspace_bytes(const vafa_absorb_args* a) {
-  (void)a;
-  return 0;
+  if (!a) return 0;
+  return absorb_fwd_ws_bytes(a, a->w_q == nullptr);
 }
 size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
   if (!a) return 0;
@@ -295,14 +353,15 @@ size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
 int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, false, false);
   if (rc) return rc;
-  const int impl = pick_impl(a->impl, false, "absorb_fwd");
+  const int impl = pick_impl(a->impl, absorb_fast(a, false).core, "absorb_fwd");
   if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, false)))) return rc;
   return absorb_fwd_simt(a, false, (cudaStream_t)stream);
 }
 int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, false);
   if (rc) return rc;
-  const int impl = pick_impl(a->impl, false, "absorb_bwd");
+  const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
   return absorb_bwd_simt(a, false, (cudaStream_t)stream);
@@ -310,14 +369,15 @@ int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
 int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, false, true);
   if (rc) return rc;
-  const int impl = pick_impl(a->impl, false, "absorb_inner_fwd");
+  const int impl = pick_impl(a->impl, absorb_fast(a, true).core, "absorb_inner_fwd");
   if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, true)))) return rc;
   return absorb_fwd_simt(a, true, (cudaStream_t)stream);
 }
 int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, true);
   if (rc) return rc;
-  const int impl = pick_impl(a->impl, false, "absorb_inner_bwd");
+  const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_inner_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
   return absorb_bwd_simt(a, true, (cudaStream_t)stream);
