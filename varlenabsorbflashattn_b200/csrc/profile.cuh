@@ -21,6 +21,7 @@ enum KernelId {
   kKAbsorbFwd,
   kKAbsorbBwd,
   kKAbsorbGemm,
+  kKAbsorbBwdDx,
   kKCount
 };
 

@@ -34,6 +34,23 @@ struct AbsorbCoreArgs {
 size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H);
 int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s);
 
+// Backward of the attention core: dU [T_q,H,256] (scaled) and dX [T_k,256] from u, X, dAlphaX
+// ([T_q,H,256], I/O dtype) and LD[t*H+h] = (lse, delta).  Needs H dividing 64.
+struct AbsorbCoreBwdArgs {
+  const void* u; const void* x; const void* dax; const void* ld;
+  void* du; void* dx;
+  const int32_t* cu_q; const int32_t* cu_k;
+  int n_seg, total_q, total_k, H, dtype;
+  float scale;
+  int sm_count;
+  void* workspace;
+  int32_t* status;
+};
+size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H);
+int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);
+int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s);
+int sm100_absorb_expand_wv(const void* w_v, void* bexp, int H, int D_H, int d_kv, int dtype, cudaStream_t s);
+
 // C[M, ldc] (16-bit) = A[M, 256] . B[256, N] with A rows K-major (row stride lda elements) and B
 // row-major [256, N] (N a multiple of 256, row stride ldb).  diag_heads > 0: row m keeps only the
 // 256/diag_heads columns of block (m % diag_heads) and writes them to C[m, 0 : 256/diag_heads]

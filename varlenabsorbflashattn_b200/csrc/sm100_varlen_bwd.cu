@@ -39,7 +39,7 @@ constexpr int kInner = 64;  // rows per inner block
 
 template <int D>
 struct BwdCfg {
-  static constexpr int kStages = (D == 128) ? 4 : 8;
+  static constexpr int kStages = (D == 128) ? 4 : (D == 64 ? 8 : 2);
   static constexpr int kSub = D / 64;
   static constexpr int kOuterSubBytes = 128 * 128;   // 128 rows x 128 B
   static constexpr int kInnerSubBytes = kInner * 128;  // 64 rows x 128 B
@@ -49,12 +49,14 @@ struct BwdCfg {
   static constexpr uint32_t kXCol = 0, kYCol = 128, kAcc0 = 256, kAcc1 = 384;
 };
 
-template <int D>
+// kAbsorb (the absorb operator, D = d_kv = 256): keys and values are the same X rows, so the dU
+// kernel has one inner operand and the dX kernel one outer operand; the unused buffer shrinks.
+template <int D, bool kDKV = false, bool kAbsorb = false>
 struct BwdSmem {
   alignas(1024) uint8_t outer_a[BwdCfg<D>::kOuterBytes];
-  alignas(1024) uint8_t outer_b[BwdCfg<D>::kOuterBytes];
+  alignas(1024) uint8_t outer_b[(kAbsorb && kDKV) ? 1024 : BwdCfg<D>::kOuterBytes];
   alignas(1024) uint8_t inner_a[BwdCfg<D>::kStages][BwdCfg<D>::kInnerBytes];
-  alignas(1024) uint8_t inner_b[BwdCfg<D>::kStages][BwdCfg<D>::kInnerBytes];
+  alignas(1024) uint8_t inner_b[BwdCfg<D>::kStages][(kAbsorb && !kDKV) ? 1024 : BwdCfg<D>::kInnerBytes];
   alignas(8) uint64_t outer_full, outer_free;
   uint64_t in_full[BwdCfg<D>::kStages], in_empty[BwdCfg<D>::kStages];
   uint64_t xy_full[2], ds_full[2], acc_done;
@@ -63,12 +65,14 @@ struct BwdSmem {
   int abort_flag;
 };
 
-static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024, "shared memory budget");
+static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024 &&
+                  sizeof(BwdSmem<256, false, true>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<256, true, true>) + 1024 <= 227 * 1024,
+              "shared memory budget");
 
 struct BwdParams {
   void* out0;            // dQ, or dV
   void* out1;            // unused, or dK
-  const float2* ld;      // [H][ld_stride] (lse with dead rows mapped to +inf, delta)
+  const float2* ld;      // varlen: [H][ld_stride]; absorb: [T_q * H] token-major.  (lse, or +inf for dead rows; delta)
   long long ld_stride;
   const SchedHeader* header;
   const WorkItem* items;
@@ -78,7 +82,14 @@ struct BwdParams {
   int32_t* status;
 };
 
-template <typename T, int D, bool kDKV>
+// kAbsorb = false: items x heads; outer/inner operands are per-head [rows, D] slices.
+// kAbsorb = true : heads are stacked into the tile rows (row = q*H + h) exactly as in the forward;
+//   dU kernel (kDKV = false): outer = (U, dAlphaX) stacked rows of 128/H queries, inner = X blocks,
+//                             S = U X^T, dP = dAlphaX X^T, dU += dS X;
+//   dX kernel (kDKV = true) : outer = 128 rows of X, inner = 64 stacked rows of (U, dAlphaX),
+//                             S^T = X U^T, dP^T = X dAlphaX^T, dX += P^T dAlphaX + (scale dS^T) U
+//                             (one accumulator; the scale is folded into dS before rounding).
+template <typename T, int D, bool kDKV, bool kAbsorb>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid_constant__ CUtensorMap tmap_outer_b,
                   const __grid_constant__ CUtensorMap tmap_inner_a, const __grid_constant__ CUtensorMap tmap_inner_b,
@@ -86,7 +97,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   using Cfg = BwdCfg<D>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
-  BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using Smem = BwdSmem<D, kDKV, kAbsorb>;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -121,7 +133,10 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   const uint32_t tbase = sm.tmem_base;
 
   const int n_items = p.header->n_items;
-  const long long total = (long long)max(n_items, 0) * p.H;
+  const int HW = kAbsorb ? 1 : p.H;
+  // inner rows (in the units of WorkItem::i_start / i_len) per 64-wide inner block
+  const int ib = (kAbsorb && kDKV) ? kInner / p.H : kInner;
+  const long long total = (long long)max(n_items, 0) * HW;
   const int G = gridDim.x, cta = blockIdx.x;
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, kDKV ? 120 : 110, n_items);
 
@@ -133,31 +148,36 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
         const long long idx = snake_index(pass, cta, G);
         if (idx >= total) continue;
-        const WorkItem w = p.items[idx / p.H];
-        const int h = (int)(idx % p.H);
-        const int nb = (w.i_len + kInner - 1) / kInner;
+        const WorkItem w = p.items[idx / HW];
+        const int h = (int)(idx % HW);
+        const int nb = (w.i_len + ib - 1) / ib;
         if (nb == 0) continue;
+        constexpr bool kOneOuter = kAbsorb && kDKV;   // dX: the X tile is both outer operands
+        constexpr bool kOneInner = kAbsorb && !kDKV;  // dU: the X block is both inner operands
         if (!mbar_wait(smem_u32(&sm.outer_free), (qi & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(smem_u32(&sm.outer_full), 2 * Cfg::kOuterBytes);
+        mbar_expect_tx(smem_u32(&sm.outer_full), (kOneOuter ? 1 : 2) * Cfg::kOuterBytes);
         for (int c = 0; c < Cfg::kSub; ++c) {
           tma_load_3d(smem_u32(sm.outer_a) + c * Cfg::kOuterSubBytes, &tmap_outer_a, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
-          tma_load_3d(smem_u32(sm.outer_b) + c * Cfg::kOuterSubBytes, &tmap_outer_b, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
+          if (!kOneOuter)
+            tma_load_3d(smem_u32(sm.outer_b) + c * Cfg::kOuterSubBytes, &tmap_outer_b, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
         }
         for (int b = 0; b < nb; ++b, ++gk) {
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
-          const int row = w.i_start + b * kInner;
+          const int row = w.i_start + b * ib;
           if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
-          mbar_expect_tx(smem_u32(&sm.in_full[st]), 2 * Cfg::kInnerBytes + (kDKV ? 66 * 8 : 0));
+          mbar_expect_tx(smem_u32(&sm.in_full[st]), (kOneInner ? 1 : 2) * Cfg::kInnerBytes + (kDKV ? 66 * 8 : 0));
           if (kDKV) {
-            // (lse, delta) pairs of rows [row, row+64): the copy starts at the even index below `row`
-            // (16-byte alignment) and takes 66 pairs; readers skip (row & 1) slots
-            const float2* src = p.ld + (long long)h * p.ld_stride + (row & ~1);
-            bulk_load_1d(smem_u32(&sm.ld[st][0]), src, 66 * 8, smem_u32(&sm.in_full[st]));
+            // (lse, delta) pairs of the block's 64 inner columns: the copy starts at the even index
+            // at or below the first pair (16-byte alignment) and takes 66 pairs; readers skip
+            // (index & 1) slots
+            const long long first = kAbsorb ? (long long)row * p.H : (long long)h * p.ld_stride + row;
+            bulk_load_1d(smem_u32(&sm.ld[st][0]), p.ld + (first & ~1LL), 66 * 8, smem_u32(&sm.in_full[st]));
           }
           for (int c = 0; c < Cfg::kSub; ++c) {
             tma_load_3d(smem_u32(sm.inner_a[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_a, smem_u32(&sm.in_full[st]), c * 64, h, row);
-            tma_load_3d(smem_u32(sm.inner_b[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_b, smem_u32(&sm.in_full[st]), c * 64, h, row);
+            if (!kOneInner)
+              tma_load_3d(smem_u32(sm.inner_b[st]) + c * Cfg::kInnerSubBytes, &tmap_inner_b, smem_u32(&sm.in_full[st]), c * 64, h, row);
           }
         }
         ++qi;
@@ -190,8 +210,9 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t offo = (kk >> 2) * Cfg::kOuterSubBytes + (kk & 3) * 32;
           const uint32_t offi = (kk >> 2) * Cfg::kInnerSubBytes + (kk & 3) * 32;
-          mma_ss(y_tmem, make_desc_sw128(smem_u32(sm.outer_b) + offo, 16, 1024),
-                 make_desc_sw128(smem_u32(sm.inner_b[st]) + offi, 16, 1024), idesc_xy, kk > 0);
+          mma_ss(y_tmem, make_desc_sw128(smem_u32((kAbsorb && kDKV) ? sm.outer_a : sm.outer_b) + offo, 16, 1024),
+                 make_desc_sw128(smem_u32((kAbsorb && !kDKV) ? sm.inner_a[st] : sm.inner_b[st]) + offi, 16, 1024), idesc_xy,
+                 kk > 0);
         }
         mma_commit(smem_u32(&sm.xy_full[g & 1]));
         if (last) mma_commit(smem_u32(&sm.outer_free));
@@ -201,8 +222,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
         const long long idx = snake_index(pass, cta, G);
         if (idx >= total) continue;
-        const WorkItem w = p.items[idx / p.H];
-        const int nb = (w.i_len + kInner - 1) / kInner;
+        const WorkItem w = p.items[idx / HW];
+        const int nb = (w.i_len + ib - 1) / ib;
         if (nb == 0) continue;
         if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break;
         tc_fence_after();
@@ -234,9 +255,9 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
                      (acc | (kk > 0)) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc1, y_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
+              mma_ts(tbase + (kAbsorb ? Cfg::kAcc0 : Cfg::kAcc1), y_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
                      make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
-                     (acc | (kk > 0)) ? 1u : 0u);
+                     (kAbsorb || acc || kk > 0) ? 1u : 0u);
           }
           mma_commit(smem_u32(&sm.in_empty[st]));
           if (b + 1 == nb) mma_commit(smem_u32(&sm.acc_done));
@@ -258,19 +279,20 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
     for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
       const long long idx = snake_index(pass, cta, G);
       if (idx >= total) continue;
-      const WorkItem w = p.items[idx / p.H];
-      const int h = (int)(idx % p.H);
-      const int nb = (w.i_len + kInner - 1) / kInner;
-      const bool row_ok = r < w.o_rows;
-      const float2* ld_h = p.ld + (long long)h * p.ld_stride;
+      const WorkItem w = p.items[idx / HW];
+      const int h = (int)(idx % HW);
+      const int nb = (w.i_len + ib - 1) / ib;
+      // valid outer rows of the tile: absorb dU stacks H heads per query row
+      const bool row_ok = r < ((kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows);
       float my_lse = INFINITY, my_delta = 0.f;
       if (!kDKV) {
         if (row_ok && nb > 0) {
-          const float2 t = ld_h[w.o_start + r];
+          const float2 t = kAbsorb ? p.ld[(long long)w.o_start * p.H + r] : p.ld[(long long)h * p.ld_stride + w.o_start + r];
           my_lse = t.x;
           my_delta = t.y;
         }
       }
+      const float ds_mul = (kAbsorb && kDKV) ? p.scale : 1.f;
 
       for (int b = 0; b < nb; ++b) {
         const uint32_t g = gk + b;
@@ -281,7 +303,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         // visibility of inner index jj = b*64 + i for this thread's outer row r
         //   dQ : jj < i_len and (causal) jj <= r + diag
         //   dKV: jj < i_len and (causal) jj >= r + diag
-        const int lim_tail = w.i_len - 1 - b * kInner;
+        const int lim_tail = (w.i_len - b * ib) * (kInner / ib) - 1;
         int lo = 0, hi = lim_tail;
         if (w.masked) {
           if (!kDKV) hi = min(hi, r + w.diag - b * kInner);
@@ -289,7 +311,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         }
         const bool need_mask = (hi < kInner - 1) || (lo > 0);
         const int st = g % S;
-        const int ld_skip = (w.i_start + b * kInner) & 1;
+        const int ld_skip = kAbsorb ? (int)(((long long)(w.i_start + b * ib) * p.H) & 1) : ((w.i_start + b * kInner) & 1);
         if (kDKV) {
           // the staged (lse, delta) block arrived with this stage's tiles (already complete here;
           // this wait only orders the reads below after the copy)
@@ -317,7 +339,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
                 delta_v = my_delta;
               }
               float pr = ex2(fmaf(__uint_as_float(xs[i + e]), c, -lse_v));
-              float ds = pr * (__uint_as_float(ys[i + e]) - delta_v);
+              float ds = pr * (__uint_as_float(ys[i + e]) - delta_v) * ds_mul;
               if (need_mask) {
                 const bool vis = (col >= lo) && (col <= hi);
                 pr = vis ? pr : 0.f;
@@ -352,11 +374,14 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         tc_fence_after();
         ++qi;
       }
-      const long long row = (long long)w.o_start + r;
+      // output row: varlen (token, head); absorb dU stacked row (token*H + head); absorb dX key row
+      const long long out_row = kAbsorb ? (kDKV ? (long long)w.o_start + r : (long long)w.o_start * p.H + r)
+                                        : ((long long)w.o_start + r) * p.H + h;
 #pragma unroll
-      for (int which = 0; which < (kDKV ? 2 : 1); ++which) {
-        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + (row * p.H + h) * D;
-        const float mul = (kDKV && which == 0) ? 1.f : p.scale;  // dV unscaled; dQ and dK scaled
+      for (int which = 0; which < ((kDKV && !kAbsorb) ? 2 : 1); ++which) {
+        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * D;
+        // dV unscaled; dQ, dK and dU scaled here; absorb dX carries the scale inside dS
+        const float mul = (kDKV && (which == 0)) ? 1.f : p.scale;
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
 #pragma unroll
         for (int c2 = 0; c2 < D / 64; ++c2) {
@@ -509,24 +534,153 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
 
   // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
   p.out0 = a->dq; p.out1 = nullptr; p.header = sq.header; p.items = sq.items;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     LaunchScope scope(kKBwdDq, s);
-    varlen_bwd_kernel<T, D, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
+    varlen_bwd_kernel<T, D, false, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
   }
   VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dQ>");
 
   // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
   p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   {
     LaunchScope scope(kKBwdDkv, s);
-    varlen_bwd_kernel<T, D, true><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
+    varlen_bwd_kernel<T, D, true, false><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
   }
   VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
   return 0;
 }
 
+
+// ---------------- absorb operator: backward core ---------------------------------------------
+// LD[t*H + h] = (lse, or +inf where the row saw no key; delta = sum_d O*dO), token-major.
+template <typename T>
+__global__ void __launch_bounds__(256) absorb_ld_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+                                                        const float* __restrict__ lse, float2* __restrict__ ld,
+                                                        long long n_rows, int D_H) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= n_rows) return;
+  const T* a = o + i * D_H;
+  const T* b = d_o + i * D_H;
+  float acc = 0.f;
+  for (int d = 0; d < D_H; ++d) acc += to_float(a[d]) * to_float(b[d]);
+  const float l = lse[i];
+  ld[i] = make_float2(l == -INFINITY ? INFINITY : l, acc);
+}
+
+// Bexp[(h',dd), (h,kv)] = W_V[kv,h,dd] if h == h' else 0: with it dAlphaX = dO . Bexp is one dense
+// product over all heads (dAlphaX[t,h,kv] = sum_dd dO[t,h,dd] W_V[kv,h,dd]).
+template <typename T>
+__global__ void __launch_bounds__(256) absorb_expand_wv_kernel(const T* __restrict__ w_v, T* __restrict__ bexp, int H, int D_H,
+                                                               int d_kv) {
+  const int n = H * d_kv;                       // columns of Bexp
+  const long long total = (long long)H * D_H * n;
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const int col = (int)(i % n), row = (int)(i / n);
+    const int h = col / d_kv, kv = col % d_kv, hp = row / D_H, dd = row % D_H;
+    bexp[i] = (h == hp) ? w_v[((long long)kv * H + h) * D_H + dd] : from_float<T>(0.f);
+  }
+}
+
+struct AbsorbBwdWs {
+  size_t hdr_du, hdr_dx, items_du, items_dx, total;
+  int cap_du, cap_dx;
+};
+
+AbsorbBwdWs absorb_bwd_ws(int total_q, int total_k, int n_seg, int H) {
+  AbsorbBwdWs w;
+  w.cap_du = total_q / (kTile / H) + n_seg + 1;
+  w.cap_dx = total_k / kTile + n_seg + 1;
+  w.hdr_du = 0;
+  w.hdr_dx = 256;
+  w.items_du = 512;
+  w.items_dx = w.items_du + align_up((size_t)w.cap_du * sizeof(WorkItem), 256);
+  w.total = w.items_dx + align_up((size_t)w.cap_dx * sizeof(WorkItem), 256);
+  return w;
+}
+
+template <typename T>
+int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
+  constexpr int D = 256;
+  const int sms = resolve_sm_count_bwd(a.sm_count);
+  const AbsorbBwdWs ws = absorb_bwd_ws(a.total_q, a.total_k, a.n_seg, a.H);
+  char* base = (char*)a.workspace;
+  int rc;
+  SchedParams sq;
+  sq.cu_q = a.cu_q; sq.cu_k = a.cu_k; sq.n_seg = a.n_seg; sq.mode = kSchedDq; sq.causal = 0; sq.H = 1;
+  sq.sm_count = sms; sq.split_len = 0; sq.tile_rows = kTile / a.H;
+  sq.cap_items = ws.cap_du; sq.cap_combine = 0; sq.cap_rows = 0;
+  sq.header = (SchedHeader*)(base + ws.hdr_du); sq.items = (WorkItem*)(base + ws.items_du); sq.combine = nullptr;
+  if ((rc = launch_scheduler(sq, s))) return rc;
+  SchedParams sk = sq;
+  sk.mode = kSchedDkv; sk.tile_rows = kTile; sk.cap_items = ws.cap_dx;
+  sk.header = (SchedHeader*)(base + ws.hdr_dx); sk.items = (WorkItem*)(base + ws.items_dx);
+  if ((rc = launch_scheduler(sk, s))) return rc;
+
+  CUtensorMap u128, g128, x64, x128, u64, g64;
+  if ((rc = encode_tmap_rows(&u128, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
+  if ((rc = encode_tmap_rows(&g128, a.dax, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
+  if ((rc = encode_tmap_rows(&x64, a.x, a.dtype, a.total_k, 1, D, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&x128, a.x, a.dtype, a.total_k, 1, D, kTile))) return rc;
+  if ((rc = encode_tmap_rows(&u64, a.u, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
+  if ((rc = encode_tmap_rows(&g64, a.dax, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
+
+  BwdParams p;
+  p.ld = (const float2*)a.ld; p.ld_stride = 0; p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
+  p.out1 = nullptr;
+  {
+    p.out0 = a.du; p.header = sq.header; p.items = sq.items;
+    const size_t smem = sizeof(BwdSmem<D, false, true>) + 1024;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(kKAbsorbBwd, s);
+    varlen_bwd_kernel<T, D, false, true><<<sms, kBwdThreads, smem, s>>>(u128, g128, x64, x64, p);
+  }
+  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<absorb dU>");
+  {
+    p.out0 = a.dx; p.header = sk.header; p.items = sk.items;
+    const size_t smem = sizeof(BwdSmem<D, true, true>) + 1024;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(kKAbsorbBwdDx, s);
+    varlen_bwd_kernel<T, D, true, true><<<sms, kBwdThreads, smem, s>>>(x128, x128, u64, g64, p);
+  }
+  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<absorb dX>");
+  return 0;
+}
+
+}  // namespace
+
+size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H) {
+  return absorb_bwd_ws(total_q, total_k, n_seg, H).total;
+}
+
+int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
+  return a.dtype == VAFA_BF16 ? launch_absorb_core_bwd<__nv_bfloat16>(a, s) : launch_absorb_core_bwd<__half>(a, s);
+}
+
+int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s) {
+  if (n_rows <= 0) return 0;
+  LaunchScope scope(kKBwdPre, s);
+  const unsigned grid = (unsigned)((n_rows + 255) / 256);
+  if (dtype == VAFA_BF16)
+    absorb_ld_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, D_H);
+  else
+    absorb_ld_kernel<__half><<<grid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, D_H);
+  VAFA_LAUNCH_CHECK("absorb_ld_kernel");
+  return 0;
+}
+
+int sm100_absorb_expand_wv(const void* w_v, void* bexp, int H, int D_H, int d_kv, int dtype, cudaStream_t s) {
+  LaunchScope scope(kKCast, s);
+  if (dtype == VAFA_BF16)
+    absorb_expand_wv_kernel<__nv_bfloat16><<<512, 256, 0, s>>>((const __nv_bfloat16*)w_v, (__nv_bfloat16*)bexp, H, D_H, d_kv);
+  else
+    absorb_expand_wv_kernel<__half><<<512, 256, 0, s>>>((const __half*)w_v, (__half*)bexp, H, D_H, d_kv);
+  VAFA_LAUNCH_CHECK("absorb_expand_wv_kernel");
+  return 0;
+}
+
+namespace {
 }  // namespace
 
 bool sm100_varlen_bwd_supported(const vafa_varlen_args* a) {

@@ -224,6 +224,26 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   return simt_gemm(g3, s);
 }
 
+// Extra backward scratch of the tcgen05 path, placed after the regions both paths share.
+struct AbsorbBwdExtra {
+  size_t ld, bexp, sched;
+};
+
+AbsorbBwdExtra absorb_bwd_extra(const vafa_absorb_args* a) {
+  AbsorbBwdExtra x;
+  const size_t H = a->num_heads;
+  x.ld = align_up(((size_t)a->total_q * H + 128) * 8, 256);
+  x.bexp = align_up(H * a->head_dim * H * a->d_kv * elem_size(a->dtype), 256);
+  x.sched = sm100_absorb_core_bwd_workspace_bytes(a->total_q, a->total_k, a->n_seg, a->num_heads);
+  return x;
+}
+
+bool absorb_bwd_core_fast(const vafa_absorb_args* a, bool inner) {
+  const AbsorbFast f = absorb_fast(a, inner);
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return f.core && f.epilogue && (64 % a->num_heads) == 0 && al(a->d_o) && al(a->dx) && al(a->dq_raw);
+}
+
 int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   const AbsorbSizes z = absorb_sizes(a);
   char* sv = (char*)a->saved;
@@ -246,15 +266,31 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
                 dq, 1, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
     if ((rc = simt_gemm(gp, s))) return rc;
   }
-  // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
-  SimtGemm g1{a->d_o, a->w_v, dax, a->dtype, a->dtype, VAFA_F32, Tq, dkv, dh, H,
-              (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
-  if ((rc = simt_gemm(g1, s))) return rc;
-  if ((rc = simt_attn_delta(a->o, a->d_o, delta, Tq, H, dh, a->dtype, s))) return rc;
-  SimtAttnParams ap = simt_from_absorb(a, u, axn);
-  ap.d_o = dax; ap.delta = delta; ap.dq = du; ap.dk = a->dx; ap.dv = nullptr;
-  if ((rc = simt_attn_dq(ap, s))) return rc;
-  if ((rc = simt_attn_dkv(ap, s))) return rc;
+  if (absorb_bwd_core_fast(a, inner)) {
+    // tcgen05 path: dAlphaX = dO . Bexp (one dense product over all heads), then the dU and dX kernels
+    const AbsorbBwdExtra x = absorb_bwd_extra(a);
+    char* ex = ws + z.dax + z.delta + z.du + z.dp;
+    void* ld = ex;
+    void* bexp = ex + x.ld;
+    void* sched = ex + x.ld + x.bexp;
+    if ((rc = sm100_absorb_expand_wv(a->w_v, bexp, H, dh, dkv, a->dtype, s))) return rc;
+    GemmNNArgs gd{a->d_o, bexp, dax, Tq, H * dkv, H * dh, H * dkv, H * dkv, a->dtype, 0, a->sm_count};
+    if ((rc = sm100_gemm_nn_k256(gd, s))) return rc;
+    if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->dtype, s))) return rc;
+    AbsorbCoreBwdArgs cb{u, a->x, dax, ld, du, a->dx, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H,
+                         a->dtype, a->scale, a->sm_count, sched, a->status};
+    if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
+  } else {
+    // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
+    SimtGemm g1{a->d_o, a->w_v, dax, a->dtype, a->dtype, VAFA_F32, Tq, dkv, dh, H,
+                (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
+    if ((rc = simt_gemm(g1, s))) return rc;
+    if ((rc = simt_attn_delta(a->o, a->d_o, delta, Tq, H, dh, a->dtype, s))) return rc;
+    SimtAttnParams ap = simt_from_absorb(a, u, axn);
+    ap.d_o = dax; ap.delta = delta; ap.dq = du; ap.dk = a->dx; ap.dv = nullptr;
+    if ((rc = simt_attn_dq(ap, s))) return rc;
+    if ((rc = simt_attn_dkv(ap, s))) return rc;
+  }
   // dW_V_h = axn_h^T dO_h                 fp32 [d_kv, H, D_H]
   SimtGemm g2{axn, a->d_o, dWV, a->dtype, a->dtype, VAFA_F32, dkv, dh, Tq, H,
               1, (int64_t)H * dkv, dkv, (int64_t)H * dh, 1, dh, (int64_t)H * dh, 1, dh, 1.f};
@@ -347,7 +383,12 @@ size_t vafa_absorb_fwd_workspace_bytes(const vafa_absorb_args* a) {
 size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
   if (!a) return 0;
   const AbsorbSizes z = absorb_sizes(a);
-  return z.dax + z.delta + z.du + z.dp;
+  size_t n = z.dax + z.delta + z.du + z.dp;
+  if (a->impl != VAFA_IMPL_SIMT && a->d_kv == 256 && a->dtype != VAFA_F32) {
+    const AbsorbBwdExtra x = absorb_bwd_extra(a);
+    n += x.ld + x.bexp + x.sched;
+  }
+  return n;
 }
 
 int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
