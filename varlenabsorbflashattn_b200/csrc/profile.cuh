@@ -22,6 +22,7 @@ enum KernelId {
   kKAbsorbBwd,
   kKAbsorbGemm,
   kKAbsorbBwdDx,
+  kKAbsorbGemmTn,
   kKCount
 };
 

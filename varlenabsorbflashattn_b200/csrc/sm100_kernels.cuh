@@ -62,4 +62,17 @@ struct GemmNNArgs {
 };
 int sm100_gemm_nn_k256(const GemmNNArgs& g, cudaStream_t s);
 
+// out[b*out_b + m*out_m + n] = sum_t A[t, (head b), m] * B[t, b*b_col_step + n], m < 256, n < n_keep
+// (fp32 result, deterministic split over tokens).  A: [T, a_heads, 256] (a_heads = 1 or batch);
+// B: [T, b_width].  (n_box, n_keep) is (256, 256) or (64, 32).
+struct GemmTNArgs {
+  const void* A; const void* B; float* out; void* workspace;
+  long long T; int dtype; int a_heads; int batch; int n_box; int n_keep; int b_width; int b_col_step;
+  long long out_b, out_m;
+  int sm_count;
+};
+size_t sm100_gemm_tn_workspace_bytes(long long T, int batch, int n_keep, int sm_count);
+int sm100_gemm_tn(const GemmTNArgs& g, cudaStream_t s);
+int sm100_transpose_square(const void* in, void* out, int n, int dtype, cudaStream_t s);
+
 }  // namespace vafa

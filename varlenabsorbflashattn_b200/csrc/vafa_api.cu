@@ -226,7 +226,7 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
 
 // Extra backward scratch of the tcgen05 path, placed after the regions both paths share.
 struct AbsorbBwdExtra {
-  size_t ld, bexp, sched;
+  size_t ld, bexp, sched, tn, wqt;
 };
 
 AbsorbBwdExtra absorb_bwd_extra(const vafa_absorb_args* a) {
@@ -235,6 +235,10 @@ AbsorbBwdExtra absorb_bwd_extra(const vafa_absorb_args* a) {
   x.ld = align_up(((size_t)a->total_q * H + 128) * 8, 256);
   x.bexp = align_up(H * a->head_dim * H * a->d_kv * elem_size(a->dtype), 256);
   x.sched = sm100_absorb_core_bwd_workspace_bytes(a->total_q, a->total_k, a->n_seg, a->num_heads);
+  const size_t t1 = sm100_gemm_tn_workspace_bytes(a->total_q, a->num_heads, 32, a->sm_count);
+  const size_t t2 = sm100_gemm_tn_workspace_bytes(a->total_q, 1, 256, a->sm_count);
+  x.tn = t1 > t2 ? t1 : t2;
+  x.wqt = align_up((size_t)256 * 256 * elem_size(a->dtype), 256);
   return x;
 }
 
@@ -260,11 +264,19 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   float* dWK = inner ? nullptr : a->dw + (size_t)dq * H * dh;
   float* dWV = inner ? a->dw : a->dw + (size_t)(dq + dkv) * H * dh;
   int rc;
+  // weight-gradient chain on the tensor-core GEMMs: needs the dU/dX fast path's preconditions, D_H = 32
+  // (the 64-column box trick of the token reductions) and, for the full operator, d_q = 256
+  const bool fast_chain = absorb_bwd_core_fast(a, inner) && dh == 32 && (inner || dq == 256);
   if (!inner && absorb_fast(a, false).prologue) {
     // the tcgen05 prologue goes straight to u; the weight-gradient chain below needs p = q_raw W_Q
-    SimtGemm gp{a->q_raw, a->w_q, sv, a->dtype, a->dtype, a->dtype, Tq, H * dh, dq, 1,
-                dq, 1, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
-    if ((rc = simt_gemm(gp, s))) return rc;
+    if (fast_chain) {
+      GemmNNArgs gp{a->q_raw, a->w_q, sv, Tq, H * dh, dq, H * dh, H * dh, a->dtype, 0, a->sm_count};
+      if ((rc = sm100_gemm_nn_k256(gp, s))) return rc;
+    } else {
+      SimtGemm gp{a->q_raw, a->w_q, sv, a->dtype, a->dtype, a->dtype, Tq, H * dh, dq, 1,
+                  dq, 1, 0, (int64_t)H * dh, 1, 0, (int64_t)H * dh, 1, 0, 1.f};
+      if ((rc = simt_gemm(gp, s))) return rc;
+    }
   }
   if (absorb_bwd_core_fast(a, inner)) {
     // tcgen05 path: dAlphaX = dO . Bexp (one dense product over all heads), then the dU and dX kernels
@@ -290,6 +302,29 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     ap.d_o = dax; ap.delta = delta; ap.dq = du; ap.dk = a->dx; ap.dv = nullptr;
     if ((rc = simt_attn_dq(ap, s))) return rc;
     if ((rc = simt_attn_dkv(ap, s))) return rc;
+  }
+  if (fast_chain) {
+    const AbsorbBwdExtra x = absorb_bwd_extra(a);
+    char* ex = ws + z.dax + z.delta + z.du + z.dp + x.ld + x.bexp + x.sched;
+    void* tn_ws = ex;
+    void* wqt = ex + x.tn;
+    // dW_V[kv,h,dd] = sum_t axn[t,h,kv] dO[t,h,dd]
+    GemmTNArgs tv{axn, a->d_o, dWV, tn_ws, Tq, a->dtype, H, H, 64, 32, H * dh, dh, dh, (long long)H * dh, a->sm_count};
+    if ((rc = sm100_gemm_tn(tv, s))) return rc;
+    if (inner) return 0;
+    // dp[(t,h), dd] = sum_kv du[t,h,kv] W_K[kv,h,dd]: stacked rows against all of W_K, own head's block kept
+    GemmNNArgs gdp{du, a->w_k, dp, (long long)Tq * H, H * dh, dkv, H * dh, dh, a->dtype, H, a->sm_count};
+    if ((rc = sm100_gemm_nn_k256(gdp, s))) return rc;
+    // dW_K[kv,h,dd] = sum_t du[t,h,kv] p[t,h,dd]
+    GemmTNArgs tk{du, p, dWK, tn_ws, Tq, a->dtype, H, H, 64, 32, H * dh, dh, dh, (long long)H * dh, a->sm_count};
+    if ((rc = sm100_gemm_tn(tk, s))) return rc;
+    // dW_Q[a,(h,dd)] = sum_t q_raw[t,a] dp[t,(h,dd)]
+    GemmTNArgs tq{a->q_raw, dp, dWQ, tn_ws, Tq, a->dtype, 1, 1, 256, 256, H * dh, 0, 0, (long long)H * dh, a->sm_count};
+    if ((rc = sm100_gemm_tn(tq, s))) return rc;
+    // dq_raw = dp W_Q^T
+    if ((rc = sm100_transpose_square(a->w_q, wqt, 256, a->dtype, s))) return rc;
+    GemmNNArgs gq{dp, wqt, a->dq_raw, Tq, dq, H * dh, dq, dq, a->dtype, 0, a->sm_count};
+    return sm100_gemm_nn_k256(gq, s);
   }
   // dW_V_h = axn_h^T dO_h                 fp32 [d_kv, H, D_H]
   SimtGemm g2{axn, a->d_o, dWV, a->dtype, a->dtype, VAFA_F32, dkv, dh, Tq, H,
@@ -386,7 +421,7 @@ size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
   size_t n = z.dax + z.delta + z.du + z.dp;
   if (a->impl != VAFA_IMPL_SIMT && a->d_kv == 256 && a->dtype != VAFA_F32) {
     const AbsorbBwdExtra x = absorb_bwd_extra(a);
-    n += x.ld + x.bexp + x.sched;
+    n += x.ld + x.bexp + x.sched + x.tn + x.wqt;
   }
   return n;
 }
