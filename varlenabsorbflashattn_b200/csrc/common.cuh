@@ -54,10 +54,14 @@ template <> __device__ __forceinline__ __half from_float<__half>(float x) { retu
 
 // Pack two floats into one 32-bit word of 16-bit values (low half = first argument).
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+// bf16 is the upper half of the fp32 pattern, so rounding is an integer add and the packing one
+// byte permute.  This keeps the conversion off the XU pipe (16 lanes/clk/SM), which the kernels
+// need for exp2; cvt.rn.bf16x2 shares that pipe and was costing as much as the exponentials.
+// Ties round away from zero instead of to even: they differ on exact ties only (1 in 2^16 values).
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-  uint32_t r;
-  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-  return r;
+  const uint32_t a = __float_as_uint(lo) + 0x8000u;
+  const uint32_t b = __float_as_uint(hi) + 0x8000u;
+  return __byte_perm(a, b, 0x7632);
 }
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   uint32_t r;

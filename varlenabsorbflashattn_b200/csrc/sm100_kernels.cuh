@@ -15,6 +15,18 @@ int sm100_varlen_bwd(const vafa_varlen_args* a, cudaStream_t s);
 // forward with the library's built-in scratch array instead of a workspace
 int sm100_varlen_fwd_noalloc(const vafa_varlen_args* a, cudaStream_t s);
 
+// The two 128 x 128-tile backward kernels (dQ, then dK/dV) on prepared tile lists and (lse, delta).
+struct Bwd128Launch {
+  const void* q; const void* k; const void* v; const void* d_o;
+  void* dq; void* dk; void* dv;
+  const void* ld; long long ld_stride;
+  const void* hdr_dq; const void* items_dq; const void* hdr_dkv; const void* items_dkv;
+  int total_q, total_k, H, D, dtype, sms;
+  float scale;
+  int32_t* status;
+};
+int sm100_varlen_bwd128_launch(const Bwd128Launch& L, cudaStream_t s);
+
 // ---- absorb operator on the tcgen05 kernels ------------------------------------------------
 // Attention core on a pre-projected u: axn[t,h,:] = softmax_h(scale * u[t,h,:] . X^T) . X, normalised,
 // in the I/O dtype; lse[t,h] log2-domain.  Requires d_kv == 256, 16-bit dtype, H dividing 128.

@@ -1,4 +1,10 @@
 // Single-CTA scheduler kernel: see sm100_sched.cuh.
+//
+// Order of the emitted work items: segments by descending total cost (bucket sort on a
+// logarithmic scale); inside a segment all heads; inside a head the tiles by descending cost and
+// their splits.  Persistent CTAs take consecutive items, so the CTAs that run at the same time
+// work on tiles of the same (segment, head) and find each other's K/V (or Q/dO) blocks in L2
+// instead of each streaming them from HBM, while the large-to-small order keeps the tail short.
 #include "sm100_sched.cuh"
 #include "profile.cuh"
 
@@ -8,52 +14,67 @@ namespace {
 constexpr int kSchedThreads = 1024;
 constexpr int kBuckets = 512;
 
-struct Unit {
-  int o_start, o_rows, i_start, i_len, diag, masked;
+struct Seg {
+  int q0, Lq, k0, Lk, off;
+  int n_tiles;  // outer tiles of the segment
 };
 
-// Visit every 128-row outer tile of every segment.  f(unit) is called by the owning thread.
-template <typename F>
-__device__ __forceinline__ void for_each_unit(const SchedParams& p, F f) {
-  for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
-    const int q0 = p.cu_q[s], Lq = p.cu_q[s + 1] - q0;
-    const int k0 = p.cu_k[s], Lk = p.cu_k[s + 1] - k0;
-    const int off = Lk - Lq;
-    if (p.mode == kSchedDkv) {
-      for (int j0 = 0; j0 < Lk; j0 += kTile) {
-        Unit u;
-        u.o_start = k0 + j0;
-        u.o_rows = min(kTile, Lk - j0);
-        int ibeg = 0;
-        if (p.causal) ibeg = max(0, j0 - off);
-        u.i_len = max(0, Lq - ibeg);
-        u.i_start = q0 + ibeg;
-        u.diag = j0 - off - ibeg;   // key row r of the tile and inner row ii: visible iff ii >= r + diag
-        u.masked = p.causal;
-        f(u);
-      }
-    } else {
-      for (int i0 = 0; i0 < Lq; i0 += p.tile_rows) {
-        Unit u;
-        u.o_start = q0 + i0;
-        u.o_rows = min(p.tile_rows, Lq - i0);
-        int kend = Lk;
-        if (p.causal) kend = min(Lk, i0 + u.o_rows + off);
-        u.i_len = max(0, kend);
-        u.i_start = k0;
-        u.diag = i0 + off;          // query row r of the tile sees inner row jj iff jj <= r + diag
-        u.masked = p.causal;
-        f(u);
-      }
-    }
-  }
-}
+struct Unit {
+  int o_start, o_rows, i_start, i_len, diag;
+};
 
 __device__ __forceinline__ int n_blocks(int len) { return (len + kTile - 1) / kTile; }
 
+__device__ __forceinline__ Seg load_seg(const SchedParams& p, int s) {
+  Seg g;
+  g.q0 = p.cu_q[s]; g.Lq = p.cu_q[s + 1] - g.q0;
+  g.k0 = p.cu_k[s]; g.Lk = p.cu_k[s + 1] - g.k0;
+  g.off = g.Lk - g.Lq;
+  g.n_tiles = (p.mode == kSchedDkv) ? (g.Lk + kTile - 1) / kTile : (g.Lq + p.tile_rows - 1) / p.tile_rows;
+  return g;
+}
+
+// Tile t of a segment, t counted in order of descending cost.
+__device__ __forceinline__ Unit make_unit(const SchedParams& p, const Seg& g, int t) {
+  Unit u;
+  if (p.mode == kSchedDkv) {
+    // key tiles; under the causal mask the first tiles see the most query rows
+    const int j0 = t * kTile;
+    u.o_start = g.k0 + j0;
+    u.o_rows = min(kTile, g.Lk - j0);
+    const int ibeg = p.causal ? max(0, j0 - g.off) : 0;
+    u.i_len = max(0, g.Lq - ibeg);
+    u.i_start = g.q0 + ibeg;
+    u.diag = j0 - g.off - ibeg;  // key row r of the tile and inner row ii: visible iff ii >= r + diag
+  } else {
+    // query tiles; under the causal mask the last tiles see the most keys
+    const int i0 = (p.causal ? (g.n_tiles - 1 - t) : t) * p.tile_rows;
+    u.o_start = g.q0 + i0;
+    u.o_rows = min(p.tile_rows, g.Lq - i0);
+    const int kend = p.causal ? min(g.Lk, i0 + u.o_rows + g.off) : g.Lk;
+    u.i_len = max(0, kend);
+    u.i_start = g.k0;
+    u.diag = i0 + g.off;         // query row r of the tile sees inner row jj iff jj <= r + diag
+  }
+  return u;
+}
+
+__device__ __forceinline__ int n_splits(int nb, int bs) { return (bs > 0 && nb > bs) ? (nb + bs - 1) / bs : 1; }
+
+// Monotone map of a cost to one of kBuckets buckets: 16 buckets per power of two.
+__device__ __forceinline__ int cost_bucket(long long c) {
+  if (c <= 0) return 0;
+  if (c < 16) return (int)c;
+  const int lz = __clzll(c);
+  const int e = 63 - lz;                                  // floor(log2 c) >= 4
+  const int m = (int)((c >> (e - 4)) & 15);               // next four bits
+  return min(kBuckets - 1, 16 * (e - 3) + m);
+}
+
 __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
   __shared__ int s_hist[kBuckets];
-  __shared__ int s_units, s_blocks, s_items, s_rows, s_bs, s_combine;
+  __shared__ int s_units, s_items, s_rows, s_bs, s_combine;
+  __shared__ long long s_blocks;
 
   if (threadIdx.x == 0) { s_units = 0; s_blocks = 0; s_combine = 0; }
   for (int b = threadIdx.x; b < kBuckets; b += kSchedThreads) s_hist[b] = 0;
@@ -61,11 +82,16 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
 
   // pass 1: totals
   {
-    int units = 0, blocks = 0;
-    for_each_unit(p, [&](const Unit& u) {
-      if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
-    });
-    if (units) { atomicAdd(&s_units, units); atomicAdd(&s_blocks, blocks); }
+    int units = 0;
+    long long blocks = 0;
+    for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
+      const Seg g = load_seg(p, s);
+      for (int t = 0; t < g.n_tiles; ++t) {
+        const Unit u = make_unit(p, g, t);
+        if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
+      }
+    }
+    if (units) { atomicAdd(&s_units, units); atomicAdd((unsigned long long*)&s_blocks, (unsigned long long)blocks); }
   }
   __syncthreads();
 
@@ -78,7 +104,7 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
       } else {
         const long long par = (long long)s_units * p.H;
         if (par > 0 && par < 2LL * p.sm_count) {
-          const long long t = ((long long)s_blocks * p.H + 2LL * p.sm_count - 1) / (2LL * p.sm_count);
+          const long long t = (s_blocks * p.H + 2LL * p.sm_count - 1) / (2LL * p.sm_count);
           bs = (int)max(8LL, t);
         }
       }
@@ -93,16 +119,19 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
     __syncthreads();
     const int bs = s_bs;
     int items = 0, rows = 0;
-    for_each_unit(p, [&](const Unit& u) {
-      const int nb = n_blocks(u.i_len);
-      const int ns = (bs > 0 && nb > bs) ? (nb + bs - 1) / bs : 1;
-      items += ns;
-      if (ns > 1) rows += ns * u.o_rows;
-    });
+    for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
+      const Seg g = load_seg(p, s);
+      for (int t = 0; t < g.n_tiles; ++t) {
+        const Unit u = make_unit(p, g, t);
+        const int ns = n_splits(n_blocks(u.i_len), bs);
+        items += ns;
+        if (ns > 1) rows += ns * u.o_rows;
+      }
+    }
     if (items) atomicAdd(&s_items, items);
     if (rows) atomicAdd(&s_rows, rows);
     __syncthreads();
-    const bool fits = (s_items <= p.cap_items) && (s_rows <= p.cap_rows);
+    const bool fits = ((long long)s_items * p.H <= p.cap_items) && (s_rows <= p.cap_rows);
     __syncthreads();
     if (fits || s_bs == 0) break;
     if (threadIdx.x == 0) s_bs = (s_bs >= (1 << 24)) ? 0 : s_bs * 2;
@@ -110,19 +139,21 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
   }
   const int bs = s_bs;
 
-  // pass 3: histogram of item costs
-  for_each_unit(p, [&](const Unit& u) {
-    const int nb = n_blocks(u.i_len);
-    const int ns = (bs > 0 && nb > bs) ? (nb + bs - 1) / bs : 1;
-    const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
-    for (int sp = 0; sp < ns; ++sp) {
-      const int b0 = sp * per;
-      const int cost = min(per, nb - b0);
-      atomicAdd(&s_hist[min(max(cost, 0), kBuckets - 1)], 1);
+  // pass 3: items per cost bucket of their segment
+  for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
+    const Seg g = load_seg(p, s);
+    long long cost = 0;
+    int items = 0;
+    for (int t = 0; t < g.n_tiles; ++t) {
+      const Unit u = make_unit(p, g, t);
+      const int nb = n_blocks(u.i_len);
+      cost += nb;
+      items += n_splits(nb, bs);
     }
-  });
+    if (items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+  }
   __syncthreads();
-  // descending exclusive scan: bucket b starts after all larger buckets
+  // descending exclusive scan: a bucket starts after all buckets of larger cost
   if (threadIdx.x == 0) {
     int run = 0;
     for (int b = kBuckets - 1; b >= 0; --b) {
@@ -136,36 +167,53 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
   __syncthreads();
   const bool overflow = s_items > p.cap_items;
 
-  // pass 4: emit
+  // pass 4: emit, one contiguous range per segment
   if (!overflow) {
-    for_each_unit(p, [&](const Unit& u) {
-      const int nb = n_blocks(u.i_len);
-      const int ns = (bs > 0 && nb > bs) ? (nb + bs - 1) / bs : 1;
-      const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
-      int base = -1;
-      if (ns > 1) {
-        base = atomicAdd(&s_rows, ns * u.o_rows);
-        const int c = atomicAdd(&s_combine, 1);
-        CombineUnit cu;
-        cu.q_start = u.o_start; cu.q_rows = u.o_rows; cu.base = base; cu.n_splits = ns;
-        p.combine[c] = cu;
+    for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
+      const Seg g = load_seg(p, s);
+      long long cost = 0;
+      int items = 0;
+      for (int t = 0; t < g.n_tiles; ++t) {
+        const int nb = n_blocks(make_unit(p, g, t).i_len);
+        cost += nb;
+        items += n_splits(nb, bs);
       }
-      for (int sp = 0; sp < ns; ++sp) {
-        const int b0 = sp * per;
-        const int cost = min(per, nb - b0);
-        const int pos = atomicAdd(&s_hist[min(max(cost, 0), kBuckets - 1)], 1);
-        WorkItem w;
-        w.o_start = u.o_start;
-        w.o_rows = u.o_rows;
-        w.i_start = u.i_start + b0 * kTile;
-        w.i_len = max(0, min(u.i_len - b0 * kTile, per * kTile));
-        w.diag = u.diag - b0 * kTile;
-        w.masked = u.masked;
-        w.partial = (ns > 1) ? base + sp * u.o_rows : -1;
-        w.cost = cost;
-        p.items[pos] = w;
+      if (items == 0) continue;
+      int pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+      for (int h = 0; h < p.H; ++h) {
+        for (int t = 0; t < g.n_tiles; ++t) {
+          const Unit u = make_unit(p, g, t);
+          const int nb = n_blocks(u.i_len);
+          const int ns = n_splits(nb, bs);
+          const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
+          int base = -1;
+          if (ns > 1 && h == 0) {
+            base = atomicAdd(&s_rows, ns * u.o_rows);
+            const int c = atomicAdd(&s_combine, 1);
+            CombineUnit cu;
+            cu.q_start = u.o_start; cu.q_rows = u.o_rows; cu.base = base; cu.n_splits = ns;
+            p.combine[c] = cu;
+          }
+          for (int sp = 0; sp < ns; ++sp) {
+            const int b0 = sp * per;
+            WorkItem w;
+            w.o_start = u.o_start;
+            w.o_rows = u.o_rows;
+            w.i_start = u.i_start + b0 * kTile;
+            w.i_len = max(0, min(u.i_len - b0 * kTile, per * kTile));
+            w.diag = u.diag - b0 * kTile;
+            w.masked = p.causal;
+            w.partial = -1;
+            // partial rows are shared by the heads ([row][head] inside the buffer): head h's item sits
+            // exactly `items` entries after head h-1's item of the same (tile, split)
+            if (ns > 1) w.partial = (h == 0) ? base + sp * u.o_rows : p.items[pos - items].partial;
+            w.head = h;
+            p.items[pos] = w;
+            ++pos;
+          }
+        }
       }
-    });
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) {

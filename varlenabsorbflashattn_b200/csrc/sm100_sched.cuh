@@ -25,7 +25,7 @@ struct alignas(16) WorkItem {
   int32_t diag;     // causal mask offset (meaning depends on the kernel, see there)
   int32_t masked;   // 1: causal mask applies inside this item
   int32_t partial;  // forward split-K: first row of this item's partial block, else -1
-  int32_t cost;     // inner blocks of 128
+  int32_t head;     // head index of this item
 };
 
 struct alignas(16) CombineUnit {
@@ -78,8 +78,8 @@ static inline SchedCaps sched_caps(int mode, int total_outer, int total_inner, i
     extra = 2LL * sm_count + 64;
     if (split_len > 0) extra += (long long)total_inner / split_len;
   }
-  long long items = units + extra;
-  if (items > (1LL << 24)) items = 1LL << 24;
+  long long items = (units + extra) * (H > 0 ? H : 1);
+  if (items > (1LL << 26)) items = 1LL << 26;
   c.cap_items = (int32_t)items;
   c.cap_combine = (int32_t)units;
   long long rows = 0;

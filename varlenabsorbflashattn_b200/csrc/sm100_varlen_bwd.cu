@@ -61,6 +61,7 @@ struct BwdSmem {
   uint64_t in_full[BwdCfg<D>::kStages], in_empty[BwdCfg<D>::kStages];
   uint64_t xy_full[2], ds_full[2], acc_done;
   alignas(16) float2 ld[BwdCfg<D>::kStages][kLdRow];  // dKV: (lse, delta) of the inner block's query rows
+  WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -104,6 +105,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    wq_init(sm.wq, 9);
     mbar_init(smem_u32(&sm.outer_full), 1);
     mbar_init(smem_u32(&sm.outer_free), 1);
     for (int i = 0; i < S; ++i) {
@@ -133,11 +135,10 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   const uint32_t tbase = sm.tmem_base;
 
   const int n_items = p.header->n_items;
-  const int HW = kAbsorb ? 1 : p.H;
   // inner rows (in the units of WorkItem::i_start / i_len) per 64-wide inner block
   const int ib = (kAbsorb && kDKV) ? kInner / p.H : kInner;
-  const long long total = (long long)max(n_items, 0) * HW;
-  const int G = gridDim.x, cta = blockIdx.x;
+  const int total = max(n_items, 0);  // one entry per head already
+  int* const next_item = const_cast<int*>(&p.header->next_item);
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, kDKV ? 120 : 110, n_items);
 
   if (warp == 8) {
@@ -145,11 +146,11 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
       bool alive = true;
-      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-        const long long idx = snake_index(pass, cta, G);
-        if (idx >= total) continue;
-        const WorkItem w = p.items[idx / HW];
-        const int h = (int)(idx % HW);
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_produce(sm.wq, n, next_item, total, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
+        const int h = w.head;
         const int nb = (w.i_len + ib - 1) / ib;
         if (nb == 0) continue;
         constexpr bool kOneOuter = kAbsorb && kDKV;   // dX: the X tile is both outer operands
@@ -219,10 +220,10 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         return true;
       };
 
-      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-        const long long idx = snake_index(pass, cta, G);
-        if (idx >= total) continue;
-        const WorkItem w = p.items[idx / HW];
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_consume_thread(sm.wq, n, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
         const int nb = (w.i_len + ib - 1) / ib;
         if (nb == 0) continue;
         if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break;
@@ -276,11 +277,11 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
     const float c = p.scale_log2;
     uint32_t gk = 0, qi = 0;
     bool alive = true;
-    for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-      const long long idx = snake_index(pass, cta, G);
-      if (idx >= total) continue;
-      const WorkItem w = p.items[idx / HW];
-      const int h = (int)(idx % HW);
+    for (uint32_t n = 0; alive; ++n) {
+      const int idx = wq_consume_warp(sm.wq, n, abort_flag);
+      if (idx < 0) break;
+      const WorkItem w = p.items[idx];
+      const int h = w.head;
       const int nb = (w.i_len + ib - 1) / ib;
       // valid outer rows of the tile: absorb dU stacks H heads per query row
       const bool row_ok = r < ((kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows);
@@ -476,7 +477,7 @@ BwdWorkspace bwd_workspace(const vafa_varlen_args* a, int sms) {
   BwdWorkspace w;
   w.caps_dq = sched_caps(kSchedDq, a->total_q, a->total_k, a->n_seg, a->num_heads, sms, 0);
   w.caps_dkv = sched_caps(kSchedDkv, a->total_k, a->total_q, a->n_seg, a->num_heads, sms, 0);
-  w.ld_stride = ((long long)a->total_q + 128 + 3) & ~3LL;  // padding: inner blocks read past the last row
+  w.ld_stride = ((long long)a->total_q + 136 + 3) & ~3LL;  // padding: inner blocks read past the last row
   w.hdr_dq = 0;
   w.hdr_dkv = 256;
   w.items_dq = 512;
@@ -517,39 +518,13 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
     VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
   }
 
-  CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
-  if ((rc = encode_tmap_rows(&q128, a->q, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&do128, a->d_o, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&k128, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&v128, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&q64, a->q, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
-  if ((rc = encode_tmap_rows(&do64, a->d_o, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
-  if ((rc = encode_tmap_rows(&k64, a->k, a->dtype, a->total_k, a->num_heads, D, kInner))) return rc;
-  if ((rc = encode_tmap_rows(&v64, a->v, a->dtype, a->total_k, a->num_heads, D, kInner))) return rc;
-
-  BwdParams p;
-  p.ld = ld; p.ld_stride = ws.ld_stride; p.H = a->num_heads;
-  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e; p.status = a->status;
-  const size_t smem = sizeof(BwdSmem<D>) + 1024;
-
-  // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
-  p.out0 = a->dq; p.out1 = nullptr; p.header = sq.header; p.items = sq.items;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    LaunchScope scope(kKBwdDq, s);
-    varlen_bwd_kernel<T, D, false, false><<<sms, kBwdThreads, smem, s>>>(q128, do128, k64, v64, p);
-  }
-  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dQ>");
-
-  // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
-  p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    LaunchScope scope(kKBwdDkv, s);
-    varlen_bwd_kernel<T, D, true, false><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
-  }
-  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
-  return 0;
+  Bwd128Launch L;
+  L.q = a->q; L.k = a->k; L.v = a->v; L.d_o = a->d_o; L.dq = a->dq; L.dk = a->dk; L.dv = a->dv;
+  L.ld = ld; L.ld_stride = ws.ld_stride;
+  L.hdr_dq = sq.header; L.items_dq = sq.items; L.hdr_dkv = sk.header; L.items_dkv = sk.items;
+  L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.D = D; L.dtype = a->dtype; L.sms = sms;
+  L.scale = a->scale; L.status = a->status;
+  return sm100_varlen_bwd128_launch(L, s);
 }
 
 

@@ -63,6 +63,7 @@ struct FwdSmem {
   uint64_t k_full[FwdCfg<D>::kStages], k_empty[FwdCfg<D>::kStages];
   uint64_t v_full[FwdCfg<D>::kStages], v_empty[FwdCfg<D>::kStages];
   uint64_t s_full[2], p_full[2], o_done;
+  WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -102,6 +103,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    wq_init(sm.wq, 5);
     mbar_init(smem_u32(&sm.q_full), 1);
     mbar_init(smem_u32(&sm.q_free), 1);
     for (int i = 0; i < S; ++i) {
@@ -132,9 +134,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const uint32_t tbase = sm.tmem_base;
 
   const int n_items = p.header->n_items;
-  const int HW = kAbsorb ? 1 : p.H;  // work units per item
-  const long long total = (long long)max(n_items, 0) * HW;
-  const int G = gridDim.x, cta = blockIdx.x;
+  const int total = max(n_items, 0);  // the item list already holds one entry per head
+  int* const next_item = const_cast<int*>(&p.header->next_item);
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, 100, n_items);
 #ifdef VAFA_TRACE
   long long tr[16];
@@ -147,11 +148,11 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
       bool alive = true;
-      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-        const long long idx = snake_index(pass, cta, G);
-        if (idx >= total) continue;
-        const WorkItem w = p.items[idx / HW];
-        const int h = (int)(idx % HW);
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_produce(sm.wq, n, next_item, total, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
+        const int h = w.head;
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
@@ -204,10 +205,10 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         return true;
       };
 
-      for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-        const long long idx = snake_index(pass, cta, G);
-        if (idx >= total) continue;
-        const WorkItem w = p.items[idx / HW];
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_consume_thread(sm.wq, n, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
         const int nb = (w.i_len + kTile - 1) / kTile;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
@@ -244,14 +245,14 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     const float c = p.scale_log2;
     uint32_t gk = 0;
     bool alive = true;
-    for (int pass = 0; alive && (long long)pass * G < total; ++pass) {
-      const long long idx = snake_index(pass, cta, G);
-      if (idx >= total) continue;
-      const WorkItem w = p.items[idx / HW];
+    for (uint32_t n = 0; alive; ++n) {
+      const int idx = wq_consume_warp(sm.wq, n, abort_flag);
+      if (idx < 0) break;
+      const WorkItem w = p.items[idx];
       const int nb = (w.i_len + kTile - 1) / kTile;
       // tile row r -> (query row of the tile, head)
       const int rq = kAbsorb ? r / p.H : r;
-      const int h = kAbsorb ? r % p.H : (int)(idx % HW);
+      const int h = kAbsorb ? r % p.H : w.head;
       const bool row_ok = rq < w.o_rows;
       float m_ref = -INFINITY, l = 0.f;
 
