@@ -24,6 +24,7 @@ struct Bwd128Launch {
   int total_q, total_k, H, D, dtype, sms;
   float scale;
   int32_t* status;
+  int run_dq, run_dkv;  // which of the two kernels to launch
 };
 int sm100_varlen_bwd128_launch(const Bwd128Launch& L, cudaStream_t s);
 

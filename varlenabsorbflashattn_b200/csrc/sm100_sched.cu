@@ -167,49 +167,76 @@ __global__ void __launch_bounds__(kSchedThreads) sched_kernel(SchedParams p) {
   __syncthreads();
   const bool overflow = s_items > p.cap_items;
 
-  // pass 4: emit, one contiguous range per segment
+  // pass 4: emit, one contiguous range per segment; one warp per segment, lanes over (head, tile)
   if (!overflow) {
-    for (int s = threadIdx.x; s < p.n_seg; s += kSchedThreads) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int s = wid; s < p.n_seg; s += kSchedThreads / 32) {
       const Seg g = load_seg(p, s);
-      long long cost = 0;
-      int items = 0;
-      for (int t = 0; t < g.n_tiles; ++t) {
-        const int nb = n_blocks(make_unit(p, g, t).i_len);
-        cost += nb;
-        items += n_splits(nb, bs);
-      }
-      if (items == 0) continue;
-      int pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
-      for (int h = 0; h < p.H; ++h) {
+      int items = 0, pos = 0, n_split_tiles = 0, c0 = 0;
+      if (lane == 0) {
+        long long cost = 0;
         for (int t = 0; t < g.n_tiles; ++t) {
-          const Unit u = make_unit(p, g, t);
-          const int nb = n_blocks(u.i_len);
+          const int nb = n_blocks(make_unit(p, g, t).i_len);
           const int ns = n_splits(nb, bs);
-          const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
-          int base = -1;
-          if (ns > 1 && h == 0) {
-            base = atomicAdd(&s_rows, ns * u.o_rows);
-            const int c = atomicAdd(&s_combine, 1);
-            CombineUnit cu;
-            cu.q_start = u.o_start; cu.q_rows = u.o_rows; cu.base = base; cu.n_splits = ns;
-            p.combine[c] = cu;
+          cost += nb;
+          items += ns;
+          n_split_tiles += (ns > 1);
+        }
+        if (items) pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+        if (n_split_tiles) {
+          // split-K bookkeeping once per tile: the partial rows are shared by the heads ([row][head])
+          c0 = atomicAdd(&s_combine, n_split_tiles);
+          int k = 0;
+          for (int t = 0; t < g.n_tiles; ++t) {
+            const Unit u = make_unit(p, g, t);
+            const int ns = n_splits(n_blocks(u.i_len), bs);
+            if (ns > 1) {
+              CombineUnit cu;
+              cu.q_start = u.o_start; cu.q_rows = u.o_rows; cu.n_splits = ns;
+              cu.base = atomicAdd(&s_rows, ns * u.o_rows);
+              p.combine[c0 + k++] = cu;
+            }
           }
-          for (int sp = 0; sp < ns; ++sp) {
-            const int b0 = sp * per;
-            WorkItem w;
-            w.o_start = u.o_start;
-            w.o_rows = u.o_rows;
-            w.i_start = u.i_start + b0 * kTile;
-            w.i_len = max(0, min(u.i_len - b0 * kTile, per * kTile));
-            w.diag = u.diag - b0 * kTile;
-            w.masked = p.causal;
-            w.partial = -1;
-            // partial rows are shared by the heads ([row][head] inside the buffer): head h's item sits
-            // exactly `items` entries after head h-1's item of the same (tile, split)
-            if (ns > 1) w.partial = (h == 0) ? base + sp * u.o_rows : p.items[pos - items].partial;
-            w.head = h;
-            p.items[pos] = w;
-            ++pos;
+        }
+      }
+      items = __shfl_sync(0xffffffffu, items, 0);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      n_split_tiles = __shfl_sync(0xffffffffu, n_split_tiles, 0);
+      c0 = __shfl_sync(0xffffffffu, c0, 0);
+      __syncwarp();
+      if (items == 0) continue;
+      if (n_split_tiles == 0) {
+        // one item per tile: position is direct
+        for (int j2 = lane; j2 < p.H * g.n_tiles; j2 += 32) {
+          const int h = j2 / g.n_tiles, t = j2 % g.n_tiles;
+          const Unit u = make_unit(p, g, t);
+          WorkItem w;
+          w.o_start = u.o_start; w.o_rows = u.o_rows; w.i_start = u.i_start; w.i_len = u.i_len;
+          w.diag = u.diag; w.masked = p.causal; w.partial = -1; w.head = h;
+          p.items[pos + h * items + t] = w;
+        }
+      } else {
+        for (int h = lane; h < p.H; h += 32) {
+          int at = pos + h * items, k = 0;
+          for (int t = 0; t < g.n_tiles; ++t) {
+            const Unit u = make_unit(p, g, t);
+            const int nb = n_blocks(u.i_len);
+            const int ns = n_splits(nb, bs);
+            const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
+            const int base = (ns > 1) ? p.combine[c0 + k++].base : -1;
+            for (int sp = 0; sp < ns; ++sp) {
+              const int b0 = sp * per;
+              WorkItem w;
+              w.o_start = u.o_start;
+              w.o_rows = u.o_rows;
+              w.i_start = u.i_start + b0 * kTile;
+              w.i_len = max(0, min(u.i_len - b0 * kTile, per * kTile));
+              w.diag = u.diag - b0 * kTile;
+              w.masked = p.causal;
+              w.partial = (ns > 1) ? base + sp * u.o_rows : -1;
+              w.head = h;
+              p.items[at++] = w;
+            }
           }
         }
       }

@@ -518,13 +518,35 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
     VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
   }
 
+  // Measured on B200 (uniform 8 x 8192 and the ragged benchmark batch): the 128-wide kernel is the
+  // faster dQ kernel (its dS has spare TMEM columns, so score MMAs overlap the element-wise work),
+  // the 64-wide kernel with double-buffered scores is the faster dK/dV kernel.
   Bwd128Launch L;
   L.q = a->q; L.k = a->k; L.v = a->v; L.d_o = a->d_o; L.dq = a->dq; L.dk = a->dk; L.dv = a->dv;
   L.ld = ld; L.ld_stride = ws.ld_stride;
   L.hdr_dq = sq.header; L.items_dq = sq.items; L.hdr_dkv = sk.header; L.items_dkv = sk.items;
   L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.D = D; L.dtype = a->dtype; L.sms = sms;
   L.scale = a->scale; L.status = a->status;
-  return sm100_varlen_bwd128_launch(L, s);
+  L.run_dq = 1; L.run_dkv = 0;
+  if ((rc = sm100_varlen_bwd128_launch(L, s))) return rc;
+
+  CUtensorMap k128, v128, q64, do64;
+  if ((rc = encode_tmap_rows(&k128, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&v128, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&q64, a->q, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&do64, a->d_o, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
+  BwdParams p;
+  p.ld = ld; p.ld_stride = ws.ld_stride; p.H = a->num_heads;
+  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e; p.status = a->status;
+  const size_t smem = sizeof(BwdSmem<D>) + 1024;
+  p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
+  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  {
+    LaunchScope scope(kKBwdDkv, s);
+    varlen_bwd_kernel<T, D, true, false><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
+  }
+  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
+  return 0;
 }
 
 

@@ -316,7 +316,11 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
             for (int e = 0; e < 2; ++e) {
               const int col = chunk * 32 + i + e;
               float lse_v, delta_v;
+#ifdef VAFA_EXP_NOLDS
+              if (false) {
+#else
               if (kDKV) {
+#endif
                 const float2 t = sm.ld[st][ld_skip + col];
                 lse_v = t.x;
                 delta_v = t.y;
@@ -444,6 +448,7 @@ static int launch128(const Bwd128Launch& L, cudaStream_t s) {
   if ((rc = encode_tmap_rows(&do128, L.d_o, L.dtype, L.total_q, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&k128, L.k, L.dtype, L.total_k, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&v128, L.v, L.dtype, L.total_k, L.H, D, 128))) return rc;
+  if (L.run_dq) {
   // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
   p.out0 = L.dq; p.out1 = nullptr; p.header = (const SchedHeader*)L.hdr_dq; p.items = (const WorkItem*)L.items_dq;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -452,6 +457,8 @@ static int launch128(const Bwd128Launch& L, cudaStream_t s) {
     varlen_bwd128_kernel<T, D, false><<<L.sms, kThreads, smem, s>>>(q128, do128, k128, v128, p);
   }
   VAFA_LAUNCH_CHECK("varlen_bwd128_kernel<dQ>");
+  }
+  if (!L.run_dkv) return 0;
   // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
   p.out0 = L.dv; p.out1 = L.dk; p.header = (const SchedHeader*)L.hdr_dkv; p.items = (const WorkItem*)L.items_dkv;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
