@@ -1,10 +1,11 @@
 // Packed variable-length attention forward for sm_100a: TMA -> shared memory -> tcgen05.mma
 // with TMEM accumulators, online softmax in registers, split-K partials + LSE combine.
 //
-// One persistent CTA per SM, 6 warps:
-//   warps 0-3  softmax + epilogue: thread t owns query row t of the 128-row tile (TMEM lane t)
-//   warp 4     TMA producer (one lane): Q tile once per item, K and V tiles through a ring
-//   warp 5     tcgen05.mma issuer (one lane) and TMEM owner
+// One persistent CTA per SM, 10 warps:
+//   warps 0-7  softmax + epilogue: two threads per query row of the 128-row tile (TMEM lane = row),
+//              each owning half of the score and output columns
+//   warp 8     TMA producer (one lane): Q tile once per item, K and V tiles through a ring
+//   warp 9     tcgen05.mma issuer (one lane) and TMEM owner
 // TMEM (512 columns): S0 [0,128), S1 [128,256) fp32 scores, double buffered; the 16-bit
 // probabilities P overwrite the first 64 columns of their S buffer; O accumulator at [256,256+D).
 //
@@ -39,12 +40,12 @@ using namespace ptx;
 #define TRACE_ADD(slot)
 #endif
 
-constexpr int kFwdThreads = 192;
+constexpr int kFwdThreads = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = (D == 128) ? 3 : (D == 64 ? 6 : 2);
+  static constexpr int kStages = (D == 128) ? 2 : (D == 64 ? 4 : 2);
   static constexpr int kSub = D / 64;                 // 64-column (128-byte) sub tiles per row
   static constexpr int kSubBytes = 128 * 128;         // one sub tile: 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;
@@ -63,6 +64,9 @@ struct FwdSmem {
   uint64_t k_full[FwdCfg<D>::kStages], k_empty[FwdCfg<D>::kStages];
   uint64_t v_full[FwdCfg<D>::kStages], v_empty[FwdCfg<D>::kStages];
   uint64_t s_full[2], p_full[2], o_done;
+  uint64_t pair_bar[4];       // the two softmax warps of one TMEM lane quadrant
+  float xmax[2][2][128];      // [block parity][half][row] partial row maxima
+  float xsum[2][128];         // [half][row] partial row sums at the end of an item
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
@@ -103,7 +107,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
-    wq_init(sm.wq, 5);
+    wq_init(sm.wq, 9);
+    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm.pair_bar[i]), 64);
     mbar_init(smem_u32(&sm.q_full), 1);
     mbar_init(smem_u32(&sm.q_free), 1);
     for (int i = 0; i < S; ++i) {
@@ -114,17 +119,17 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.s_full[i]), 1);
-      mbar_init(smem_u32(&sm.p_full[i]), 128);
+      mbar_init(smem_u32(&sm.p_full[i]), 256);
     }
     mbar_init(smem_u32(&sm.o_done), 1);
     fence_barrier_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == 8 && lane == 0) {
     prefetch_tensormap(&tmap_q);
     prefetch_tensormap(&tmap_k);
     prefetch_tensormap(&tmap_v);
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(smem_u32(&sm.tmem_base), Cfg::kTmemCols);
     tmem_relinquish();
   }
@@ -143,7 +148,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   const long long t_begin = clock64();
 #endif
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
@@ -177,7 +182,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ++qi;
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -229,7 +234,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int kk = 0; kk < kTile / 16; ++kk) {
             // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart
             const uint64_t db = make_desc_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]) + kk * 2048, Cfg::kSubBytes, 1024);
-            mma_ts(tbase + Cfg::kOCol, a_tmem + kk * 8, db, idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
+            mma_ts(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, db, idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
           }
           mma_commit(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.v_empty[st]));
           mma_commit(smem_u32(&sm.o_done));
@@ -239,9 +244,16 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
     }
   } else {
-    // ---------------- softmax + epilogue (warps 0-3) ----------------
-    const int r = threadIdx.x;  // row of the tile == TMEM lane
-    const uint32_t lane_base = tbase + ((uint32_t)(warp * 32) << 16);
+    // ---------------- softmax + epilogue (warps 0-7) ----------------
+    // Two threads per tile row: thread (r, half) owns score columns [64*half, 64*half+64) of every
+    // block and output columns [D/2*half, D/2*(half+1)).  The two halves of a row sit in warps w and
+    // w+4 (same TMEM lane quadrant) and exchange their partial row maximum through shared memory;
+    // two warps per scheduler also give the exp2-heavy loop a second instruction stream to overlap.
+    const int r = threadIdx.x & 127;
+    const int half = threadIdx.x >> 7;
+    const uint32_t pair_bar = smem_u32(&sm.pair_bar[warp & 3]);
+    uint32_t pair_cnt = 0;
+    const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     const float c = p.scale_log2;
     uint32_t gk = 0;
     bool alive = true;
@@ -254,7 +266,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int rq = kAbsorb ? r / p.H : r;
       const int h = kAbsorb ? r % p.H : w.head;
       const bool row_ok = rq < w.o_rows;
-      float m_ref = -INFINITY, l = 0.f;
+      float m_ref = -INFINITY, l = 0.f;  // l: sum over this thread's columns only
 
       for (int b = 0; b < nb; ++b) {
         const uint32_t g = gk + b;
@@ -263,44 +275,45 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #ifdef VAFA_TRACE
         const long long t_sm0 = clock64();
 #endif
-        const uint32_t s_addr = lane_base + (g & 1) * 128;
-        float s[128];
+        const uint32_t s_addr = lane_base + (g & 1) * 128 + half * 64;
+        float s[64];
         {
-          uint32_t t0[32], t1[32], t2[32], t3[32];
+          uint32_t t0[32], t1[32];
           tmem_ld32(s_addr + 0, t0);
           tmem_ld32(s_addr + 32, t1);
-          tmem_ld32(s_addr + 64, t2);
-          tmem_ld32(s_addr + 96, t3);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             s[i] = __uint_as_float(t0[i]);
             s[32 + i] = __uint_as_float(t1[i]);
-            s[64 + i] = __uint_as_float(t2[i]);
-            s[96 + i] = __uint_as_float(t3[i]);
           }
         }
-        // mask: inner index jj = b*128 + i is visible iff jj < i_len and (causal) jj <= r + diag
+        // mask: inner index jj = b*128 + col is visible iff jj < i_len and (causal) jj <= r + diag
         const int lim_tail = w.i_len - 1 - b * kTile;
         const int lim_diag = w.masked ? (w.diag - b * kTile) : 0x3fffffff;  // for row 0
         if (lim_tail < kTile - 1 || lim_diag < kTile - 1) {
-          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff);
+          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff) - half * 64;
 #pragma unroll
-          for (int i = 0; i < 128; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
+          for (int i = 0; i < 64; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
         }
-        // row maximum: eight independent chains of 3-input max (one warp per scheduler has no
-        // other warp to hide a serial chain's latency behind)
+        // row maximum of this half: eight independent chains of 3-input max
         float m8[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) m8[j] = max3(s[j], s[8 + j], s[16 + j]);
+        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(s[j2], s[8 + j2], s[16 + j2]);
 #pragma unroll
-        for (int i = 24; i < 120; i += 16) {
+        for (int i = 24; i < 56; i += 16) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) m8[j] = max3(m8[j], s[i + j], s[i + 8 + j]);
+          for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(m8[j2], s[i + j2], s[i + 8 + j2]);
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) m8[j] = fmaxf(m8[j], s[120 + j]);
-        const float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
+        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = fmaxf(m8[j2], s[56 + j2]);
+        float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
+        // combine with the other half of the row
+        sm.xmax[g & 1][half][r] = mx;
+        mbar_arrive(pair_bar);
+        if (!mbar_wait(pair_bar, pair_cnt & 1, abort_flag)) { alive = false; break; }
+        ++pair_cnt;
+        mx = fmaxf(mx, sm.xmax[g & 1][half ^ 1][r]);
         const float m_blk = mx * c;  // c > 0
         float m_new = fmaxf(m_ref, m_blk);
         const bool resc = m_new > m_ref + kRescaleThreshold;
@@ -308,9 +321,9 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const float alpha = resc ? ex2(m_ref - m_new) : 1.f;
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t pk[64];
+        uint32_t pk[32];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 32; ++i) {
           const float p0 = ex2(fmaf(s[2 * i], c, -m_use));
           const float p1 = ex2(fmaf(s[2 * i + 1], c, -m_use));
           sum4[i & 3] += p0 + p1;
@@ -318,13 +331,9 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_ref = m_new;
-        {
-          uint32_t a0[32], a1[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) { a0[i] = pk[i]; a1[i] = pk[32 + i]; }
-          tmem_st32(s_addr + 0, a0);
-          tmem_st32(s_addr + 32, a1);
-        }
+        // 64 probabilities -> 32 packed columns over the first half of the columns just read; the MMA
+        // issuer addresses K-step kk at column (kk/4)*64 + (kk%4)*8
+        tmem_st32(s_addr, pk);
         if (b > 0) {
 #ifdef VAFA_TRACE
           tr[10] += clock64() - t_sm0;
@@ -332,11 +341,9 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done), (g - 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
           tc_fence_after();
           if (__any_sync(0xffffffffu, resc)) {
-#ifdef VAFA_TRACE
-            tr[12] += 1;
-#endif
 #pragma unroll
-            for (int cc = 0; cc < D / 32; ++cc) {
+            for (int c2 = 0; c2 < D / 64; ++c2) {
+              const int cc = half * (D / 64) + c2;
               uint32_t t[32];
               tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
               tmem_wait_ld();
@@ -355,23 +362,27 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       }
       if (!alive) break;
       gk += nb;
-#ifdef VAFA_TRACE
-      const long long t_ep0 = clock64();
-#endif
 
       // ---- epilogue ----
+      float l_tot = 0.f;
       if (nb > 0) {
         if (!mbar_wait(smem_u32(&sm.o_done), (gk - 1) & 1, abort_flag)) break;
         tc_fence_after();
+        sm.xsum[half][r] = l;
+        mbar_arrive(pair_bar);
+        if (!mbar_wait(pair_bar, pair_cnt & 1, abort_flag)) break;
+        ++pair_cnt;
+        l_tot = l + sm.xsum[half ^ 1][r];
       }
-      const bool dead = (nb == 0) || !(l > 0.f);
-      const float inv_l = dead ? 0.f : 1.f / l;
-      const float lse_val = dead ? -INFINITY : m_ref + log2f(l);
+      const bool dead = (nb == 0) || !(l_tot > 0.f);
+      const float inv_l = dead ? 0.f : 1.f / l_tot;
+      const float lse_val = dead ? -INFINITY : m_ref + log2f(l_tot);
       if (w.partial < 0) {
         const long long row = (long long)w.o_start + rq;
         T* optr = reinterpret_cast<T*>(p.o) + (row * p.H + h) * D;
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int c2 = 0; c2 < D / 64; ++c2) {
+          const int cc = half * (D / 64) + c2;
           uint32_t t[32];
           if (nb > 0) {
             tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
@@ -393,12 +404,13 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
         }
-        if (row_ok) p.lse[row * p.H + h] = lse_val;
+        if (row_ok && half == 0) p.lse[row * p.H + h] = lse_val;
       } else {
         const long long prow = (long long)w.partial + rq;
         float* optr = p.partial_o + (prow * p.H + h) * D;
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int c2 = 0; c2 < D / 64; ++c2) {
+          const int cc = half * (D / 64) + c2;
           uint32_t t[32];
           if (nb > 0) {
             tmem_ld32(lane_base + Cfg::kOCol + cc * 32, t);
@@ -420,21 +432,15 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
         }
-        if (row_ok) p.partial_lse[prow * p.H + h] = lse_val;
+        if (row_ok && half == 0) p.partial_lse[prow * p.H + h] = lse_val;
       }
-#ifdef VAFA_TRACE
-      tr[13] += clock64() - t_ep0;
-      tr[14] += 1;
-#endif
-      // the TMEM reads of O above must finish before the next item's first P.V overwrites O;
-      // that MMA is issued only after this thread's next p_full arrival, which follows in
-      // program order (tcgen05.wait::ld has completed every read).
+      // the TMEM reads of O above finish (tcgen05.wait::ld) before this thread's next p_full arrival,
+      // and the next item's first P.V, which overwrites O, is issued only after that arrival
     }
   }
 
-  // ---------------- teardown ----------------
 #ifdef VAFA_TRACE
-  if (p.trace != nullptr && (threadIdx.x == 0 || threadIdx.x == 128 || threadIdx.x == 160)) {
+  if (p.trace != nullptr && (threadIdx.x == 0 || threadIdx.x == 256 || threadIdx.x == 288)) {
     tr[15] = clock64() - t_begin;
     for (int i = 0; i < 16; ++i)
       if (tr[i] != 0) p.trace[(long long)blockIdx.x * 16 + i] = tr[i];
@@ -449,7 +455,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     while (clock64() - t0 < 200000) { }
     __syncthreads();
   }
-  if (warp == 5) tmem_dealloc(tbase, Cfg::kTmemCols);
+  if (warp == 9) tmem_dealloc(tbase, Cfg::kTmemCols);
 }
 
 // ---------------- split-K combine -------------------------------------------------------------
