@@ -200,20 +200,21 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         tc_fence_after();
         const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
         const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
+        const uint32_t oa_lo = desc_lo_sw128(smem_u32(sm.outer_a), 16);
+        const uint32_t ob_lo = desc_lo_sw128(smem_u32((kAbsorb && kDKV) ? sm.outer_a : sm.outer_b), 16);
+        const uint32_t ia_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), 16);
+        const uint32_t ib_lo = desc_lo_sw128(smem_u32((kAbsorb && !kDKV) ? sm.inner_a[st] : sm.inner_b[st]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offo = (kk >> 2) * Cfg::kOuterSubBytes + (kk & 3) * 32;
-          const uint32_t offi = (kk >> 2) * Cfg::kInnerSubBytes + (kk & 3) * 32;
-          mma_ss(x_tmem, make_desc_sw128(smem_u32(sm.outer_a) + offo, 16, 1024),
-                 make_desc_sw128(smem_u32(sm.inner_a[st]) + offi, 16, 1024), idesc_xy, kk > 0);
+          const uint32_t offo = (kk >> 2) * (Cfg::kOuterSubBytes >> 4) + (kk & 3) * 2;  // 16-byte units
+          const uint32_t offi = (kk >> 2) * (Cfg::kInnerSubBytes >> 4) + (kk & 3) * 2;
+          mma_ss2(x_tmem, oa_lo + offo, ia_lo + offi, idesc_xy, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t offo = (kk >> 2) * Cfg::kOuterSubBytes + (kk & 3) * 32;
-          const uint32_t offi = (kk >> 2) * Cfg::kInnerSubBytes + (kk & 3) * 32;
-          mma_ss(y_tmem, make_desc_sw128(smem_u32((kAbsorb && kDKV) ? sm.outer_a : sm.outer_b) + offo, 16, 1024),
-                 make_desc_sw128(smem_u32((kAbsorb && !kDKV) ? sm.inner_a[st] : sm.inner_b[st]) + offi, 16, 1024), idesc_xy,
-                 kk > 0);
+          const uint32_t offo = (kk >> 2) * (Cfg::kOuterSubBytes >> 4) + (kk & 3) * 2;
+          const uint32_t offi = (kk >> 2) * (Cfg::kInnerSubBytes >> 4) + (kk & 3) * 2;
+          mma_ss2(y_tmem, ob_lo + offo, ib_lo + offi, idesc_xy, kk > 0);
         }
         mma_commit(smem_u32(&sm.xy_full[g & 1]));
         if (last) mma_commit(smem_u32(&sm.outer_free));
@@ -240,25 +241,24 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
           const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
           const uint32_t acc = (b > 0) ? 1u : 0u;
+          const uint32_t ma_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), Cfg::kInnerSubBytes);
+          const uint32_t mb_lo = desc_lo_sw128(smem_u32((kAbsorb && !kDKV) ? sm.inner_a[st] : sm.inner_b[st]), Cfg::kInnerSubBytes);
           if (!kDKV) {
             // dQ += dS . K_g     (dS in X, 16-bit packed; K block MN-major)
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
-                     make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
-                     (acc | (kk > 0)) ? 1u : 0u);
+              mma_ts2(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8, ma_lo + kk * (2048 >> 4), idesc_acc,
+                      (acc | (kk > 0)) ? 1u : 0u);
           } else {
             // dV += P^T . dO_g ;  dK += dS^T . Q_g
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
-                     make_desc_sw128(smem_u32(sm.inner_b[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
-                     (acc | (kk > 0)) ? 1u : 0u);
+              mma_ts2(tbase + Cfg::kAcc0, x_tmem + (kk >> 1) * 32 + (kk & 1) * 8, mb_lo + kk * (2048 >> 4), idesc_acc,
+                      (acc | (kk > 0)) ? 1u : 0u);
 #pragma unroll
             for (int kk = 0; kk < kInner / 16; ++kk)
-              mma_ts(tbase + (kAbsorb ? Cfg::kAcc0 : Cfg::kAcc1), y_tmem + (kk >> 1) * 32 + (kk & 1) * 8,
-                     make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kInnerSubBytes, 1024), idesc_acc,
-                     (kAbsorb || acc || kk > 0) ? 1u : 0u);
+              mma_ts2(tbase + (kAbsorb ? Cfg::kAcc0 : Cfg::kAcc1), y_tmem + (kk >> 1) * 32 + (kk & 1) * 8, ma_lo + kk * (2048 >> 4),
+                      idesc_acc, (kAbsorb || acc || kk > 0) ? 1u : 0u);
           }
           mma_commit(smem_u32(&sm.in_empty[st]));
           if (b + 1 == nb) mma_commit(smem_u32(&sm.acc_done));

@@ -180,17 +180,17 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.in_full[st]), (g / S) & 1, abort_flag)) return false; TRACE_ADD(4); }
         tc_fence_after();
         TRACE_T0();
+        const uint32_t oa_lo = desc_lo_sw128(smem_u32(sm.outer_a), 16), ob_lo = desc_lo_sw128(smem_u32(sm.outer_b), 16);
+        const uint32_t ia_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), 16), ib_lo = desc_lo_sw128(smem_u32(sm.inner_b[st]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-          mma_ss(tbase + Cfg::kX, make_desc_sw128(smem_u32(sm.outer_a) + off, 16, 1024),
-                 make_desc_sw128(smem_u32(sm.inner_a[st]) + off, 16, 1024), idesc_xy, kk > 0);
+          const uint32_t off = (kk >> 2) * (Cfg::kSubBytes >> 4) + (kk & 3) * 2;  // 16-byte units
+          mma_ss2(tbase + Cfg::kX, oa_lo + off, ia_lo + off, idesc_xy, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-          mma_ss(tbase + Cfg::kY, make_desc_sw128(smem_u32(sm.outer_b) + off, 16, 1024),
-                 make_desc_sw128(smem_u32(sm.inner_b[st]) + off, 16, 1024), idesc_xy, kk > 0);
+          const uint32_t off = (kk >> 2) * (Cfg::kSubBytes >> 4) + (kk & 3) * 2;
+          mma_ss2(tbase + Cfg::kY, ob_lo + off, ib_lo + off, idesc_xy, kk > 0);
         }
         mma_commit(smem_u32(&sm.xy_full));
         if (last) mma_commit(smem_u32(&sm.outer_free));
@@ -201,25 +201,24 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         const int st = g % S;
         const uint32_t acc = first ? 0u : 1u;
         TRACE_T0();
+        const uint32_t ma_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), Cfg::kSubBytes);
+        const uint32_t mb_lo = desc_lo_sw128(smem_u32(sm.inner_b[st]), Cfg::kSubBytes);
         if (!kDKV) {
           // dQ += dS . K_g   (dS: 16-bit, contiguous in its buffer; K block MN-major)
           const uint32_t ds_tmem = tbase + Cfg::kAcc1 + (g & 1) * 64;
 #pragma unroll
           for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts(tbase + Cfg::kAcc0, ds_tmem + kk * 8, make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kSubBytes, 1024),
-                   idesc_acc, (acc | (kk > 0)) ? 1u : 0u);
+            mma_ts2(tbase + Cfg::kAcc0, ds_tmem + kk * 8, ma_lo + kk * (2048 >> 4), idesc_acc, (acc | (kk > 0)) ? 1u : 0u);
         } else {
           // dV += P^T . dO_g ;  dK += dS^T . Q_g   (K-step kk sits at column (kk/2)*32 + (kk%2)*8)
 #pragma unroll
           for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts(tbase + Cfg::kAcc0, tbase + Cfg::kX + (kk >> 1) * 32 + (kk & 1) * 8,
-                   make_desc_sw128(smem_u32(sm.inner_b[st]) + kk * 2048, Cfg::kSubBytes, 1024), idesc_acc,
-                   (acc | (kk > 0)) ? 1u : 0u);
+            mma_ts2(tbase + Cfg::kAcc0, tbase + Cfg::kX + (kk >> 1) * 32 + (kk & 1) * 8, mb_lo + kk * (2048 >> 4), idesc_acc,
+                    (acc | (kk > 0)) ? 1u : 0u);
 #pragma unroll
           for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts(tbase + Cfg::kAcc1, tbase + Cfg::kY + (kk >> 1) * 32 + (kk & 1) * 8,
-                   make_desc_sw128(smem_u32(sm.inner_a[st]) + kk * 2048, Cfg::kSubBytes, 1024), idesc_acc,
-                   (acc | (kk > 0)) ? 1u : 0u);
+            mma_ts2(tbase + Cfg::kAcc1, tbase + Cfg::kY + (kk >> 1) * 32 + (kk & 1) * 8, ma_lo + kk * (2048 >> 4), idesc_acc,
+                    (acc | (kk > 0)) ? 1u : 0u);
         }
         mma_commit(smem_u32(&sm.in_empty[st]));
         if (last) mma_commit(smem_u32(&sm.acc_done));

@@ -197,12 +197,12 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.k_full[st]), ph, abort_flag)) return false; TRACE_ADD(4); }
         tc_fence_after();
         const uint32_t d_tmem = tbase + (g & 1) * 128;
+        const uint32_t q_lo = desc_lo_sw128(smem_u32(sm.q), 16), k_lo = desc_lo_sw128(smem_u32(sm.k[st]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Cfg::kSubBytes + (kk & 3) * 32;
-          const uint64_t da = make_desc_sw128(smem_u32(sm.q) + off, 16, 1024);
-          const uint64_t db = make_desc_sw128(smem_u32(sm.k[st]) + off, 16, 1024);
-          mma_ss(d_tmem, da, db, idesc_qk, kk > 0);
+          constexpr int kSubStep = Cfg::kSubBytes >> 4;
+          const uint32_t off = (kk >> 2) * kSubStep + (kk & 3) * 2;  // in 16-byte units
+          mma_ss2(d_tmem, q_lo + off, k_lo + off, idesc_qk, kk > 0);
         }
         if (!kAbsorb) mma_commit(smem_u32(&sm.k_empty[st]));  // absorb: the tile is still needed for P.X
         mma_commit(smem_u32(&sm.s_full[g & 1]));
@@ -230,12 +230,12 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           if (!kAbsorb) { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
           tc_fence_after();
           const uint32_t a_tmem = tbase + (g & 1) * 128;
+          // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart (the LBO)
+          const uint32_t v_lo = desc_lo_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]), Cfg::kSubBytes);
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk) {
-            // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart
-            const uint64_t db = make_desc_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]) + kk * 2048, Cfg::kSubBytes, 1024);
-            mma_ts(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, db, idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, v_lo + kk * (2048 >> 4), idesc_pv,
+                    (b > 0 || kk > 0) ? 1u : 0u);
           mma_commit(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.v_empty[st]));
           mma_commit(smem_u32(&sm.o_done));
         }
