@@ -15,6 +15,11 @@ namespace vafa {
 int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows, int heads, int dim, int box_rows,
                      int box_heads = 1);
 
+// Tensor map over the fold array [rows, heads, 32] of 16-bit elements (see sm100_varlen_bwd128.cu):
+// box = 16 elements x 1 head x 128 rows with the 32-byte swizzle, so one copy fills one K = 16 operand
+// tile of 128 rows x 32 B.
+int encode_tmap_fold(CUtensorMap* m, const void* base, int dtype, long long rows, int heads);
+
 // Dynamic work distribution inside a persistent CTA.  The TMA-producer thread draws the next item
 // index from a global counter and publishes it through a small shared-memory ring; the other roles
 // (MMA issuer, element-wise warps) read the same sequence.  Items are handed out in list order, so

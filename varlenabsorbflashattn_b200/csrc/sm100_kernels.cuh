@@ -20,6 +20,7 @@ struct Bwd128Launch {
   const void* q; const void* k; const void* v; const void* d_o;
   void* dq; void* dk; void* dv;
   const void* ld; long long ld_stride;
+  const void* aug;  // fold array [total_q, H, 32] (dK/dV kernel)
   const void* hdr_dq; const void* items_dq; const void* hdr_dkv; const void* items_dkv;
   int total_q, total_k, H, D, dtype, sms;
   float scale;

@@ -47,4 +47,20 @@ int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows
   return 0;
 }
 
+int encode_tmap_fold(CUtensorMap* m, const void* base, int dtype, long long rows, int heads) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return fail(VAFA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if (dtype != VAFA_BF16 && dtype != VAFA_F16) return fail(VAFA_ERR_UNSUPPORTED, "tensor maps are built for 16-bit types only");
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(VAFA_ERR_INVALID, "tensor base must be 16-byte aligned");
+  cuuint64_t dims[3] = {32, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
+  cuuint64_t strides[2] = {64, (cuuint64_t)heads * 64};
+  cuuint32_t box[3] = {16, 1, 128};
+  cuuint32_t es[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == VAFA_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = enc(m, dt, 3, const_cast<void*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(VAFA_ERR_CUDA, "cuTensorMapEncodeTiled (fold) failed with %d", (int)r);
+  return 0;
+}
+
 }  // namespace vafa

@@ -1,18 +1,18 @@
-// Packed variable-length attention backward for sm_100a (tcgen05 + TMA + TMEM).
+// Packed variable-length attention backward for sm_100a: host side (tile lists, preprocess kernel,
+// launch of the 128 x 128-tile dQ and dK/dV kernels of sm100_varlen_bwd128.cu), and the 64-row-block
+// kernel template that the absorb operator's backward core (D = d_kv = 256) runs on.
 //
-// Three kernels, no atomics, so gradients are run-to-run identical:
+// Three kernels per backward, no atomics, so gradients are run-to-run identical:
 //   1. preprocess: delta[t,h] = sum_d O*dO (fp32), written together with the LSE as float2
-//      pairs in a head-major array LD[h][t] = (lse, delta)  (reference: kernels.py:186-216)
-//   2. dQ kernel : one 128-row query tile per item, walks the segment's keys in 64-row blocks
-//      (reference: kernels.py:233-350)
-//   3. dKV kernel: one 128-row key tile per item, walks the segment's query rows in 64-row
-//      blocks (reference: kernels.py:367-494)
+//      pairs in a head-major array LD[h][t] = (lse, delta)  (reference: kernels.py:186-216), and as
+//      16-bit fold rows for the dK/dV kernel
+//   2. dQ kernel : one 128-row query tile per item, walks the segment's keys (reference: kernels.py:233-350)
+//   3. dKV kernel: one 128-row key tile per item, walks the segment's query rows (reference: kernels.py:367-494)
 // (paths: triton_fa_varlen_v2/triton_fa_varlen_v2/kernels.py)
 //
-// Kernels 2 and 3 are one template.  "Outer" is the 128-row tile that stays in shared memory
-// (two operands: Q,dO or K,V), "inner" the 64-row blocks streamed through a ring (K,V or Q,dO).
-// Per inner block g, with X/Y double buffered in TMEM so the next block's scores are computed
-// while the current block's element-wise work runs:
+// The 64-row-block template.  "Outer" is the 128-row tile that stays in shared memory, "inner" the
+// 64-row blocks streamed through a ring.  Per inner block g, with X/Y double buffered in TMEM so the
+// next block's scores are computed while the current block's element-wise work runs:
 //     X[g&1] = outerA . innerA^T        (S   = Q K^T      or  S^T  = K Q^T)
 //     Y[g&1] = outerB . innerB^T        (dP  = dO V^T     or  dP^T = V dO^T)
 //   compute warps (thread = outer row):  P = 2^(X c - lse),  dS = P (Y - delta)
@@ -318,7 +318,10 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           // this wait only orders the reads below after the copy)
           if (!mbar_wait(smem_u32(&sm.in_full[st]), (g / S) & 1, abort_flag)) { alive = false; break; }
         }
-        {
+        // masked blocks (tails, the causal diagonal) take their own copy of the loop; the choice is
+        // warp-uniform because the TMEM loads and stores inside are .sync.aligned
+        auto block_body = [&](auto mask_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
           uint32_t xs[32], ys[32];
           tmem_ld32(x_addr + half * 32, xs);
           tmem_ld32(y_addr + half * 32, ys);
@@ -341,7 +344,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
               }
               float pr = ex2(fmaf(__uint_as_float(xs[i + e]), c, -lse_v));
               float ds = pr * (__uint_as_float(ys[i + e]) - delta_v) * ds_mul;
-              if (need_mask) {
+              if (kMask) {
                 const bool vis = (col >= lo) && (col <= hi);
                 pr = vis ? pr : 0.f;
                 ds = vis ? ds : 0.f;
@@ -361,7 +364,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             tmem_st16(x_addr + half * 32, pp);
             tmem_st16(y_addr + half * 32, dd);
           }
-        }
+        };
+        if (__any_sync(0xffffffffu, need_mask)) block_body(std::true_type{}); else block_body(std::false_type{});
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.ds_full[g & 1]));
@@ -424,10 +428,31 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   if (warp == 5) tmem_dealloc(tbase, Cfg::kTmemCols);
 }
 
-// delta = rowsum(O * dO); LD[h][t] = (lse or +inf for rows that saw no key, delta).
+// A value as three 16-bit pieces (hi, mid, lo) whose exact sum, times 1 (bf16) or 64 (fp16), gives it
+// back to about 24 bits: the operand rows of the fold step of the dK/dV kernel.  Non-finite values keep
+// only the first piece (-inf stays -inf under the sum).  fp16 pieces are stored divided by 64 so that
+// values up to 4.2e6 stay in range; larger ones saturate.
+template <typename T>
+__device__ __forceinline__ uint2 fold_pieces(float a) {
+  constexpr bool kBf = std::is_same<T, __nv_bfloat16>::value;
+  if (!kBf) a = isfinite(a) ? fminf(fmaxf(a * (1.f / 64.f), -65504.f), 65504.f) : a;
+  const T hi = from_float<T>(a);
+  T mid = from_float<T>(0.f), lo = mid;
+  if (isfinite(a)) {
+    const float r1 = a - to_float(hi);
+    mid = from_float<T>(r1);
+    lo = from_float<T>(r1 - to_float(mid));
+  }
+  auto bits = [](T x) -> uint32_t { return (uint32_t)(*reinterpret_cast<const unsigned short*>(&x)); };
+  return make_uint2(bits(hi) | (bits(mid) << 16), bits(lo));
+}
+
+// delta = rowsum(O * dO); LD[h][t] = (lse or +inf for rows that saw no key, delta); and the same two
+// numbers as fold rows fold[t][h][0:16] = pieces(-lse / c), fold[t][h][16:32] = pieces(-delta).
 template <typename T, int D>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                              const float* __restrict__ lse, float2* __restrict__ ld,
+                                                             uint4* __restrict__ fold, float inv_c,
                                                              long long ld_stride, int total_q, int H) {
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
@@ -456,11 +481,18 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const T* __restrict
   if (lane == 0) {
     const float l = lse[w];
     ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
+    const uint2 fl = fold_pieces<T>(l == -INFINITY ? -INFINITY : -l * inv_c);
+    const uint2 fd = fold_pieces<T>(-part);
+    uint4* dst = fold + w * 4;  // 32 elements = 64 B per (token, head)
+    dst[0] = make_uint4(fl.x, fl.y, 0u, 0u);
+    dst[1] = make_uint4(0u, 0u, 0u, 0u);
+    dst[2] = make_uint4(fd.x, fd.y, 0u, 0u);
+    dst[3] = make_uint4(0u, 0u, 0u, 0u);
   }
 }
 
 struct BwdWorkspace {
-  size_t hdr_dq, hdr_dkv, items_dq, items_dkv, ld, total;
+  size_t hdr_dq, hdr_dkv, items_dq, items_dkv, ld, fold, total;
   SchedCaps caps_dq, caps_dkv;
   long long ld_stride;
 };
@@ -483,7 +515,8 @@ BwdWorkspace bwd_workspace(const vafa_varlen_args* a, int sms) {
   w.items_dq = 512;
   w.items_dkv = w.items_dq + align_up((size_t)w.caps_dq.cap_items * sizeof(WorkItem), 256);
   w.ld = w.items_dkv + align_up((size_t)w.caps_dkv.cap_items * sizeof(WorkItem), 256);
-  w.total = w.ld + align_up((size_t)a->num_heads * w.ld_stride * sizeof(float2), 256);
+  w.fold = w.ld + align_up((size_t)a->num_heads * w.ld_stride * sizeof(float2), 256);
+  w.total = w.fold + align_up((size_t)a->total_q * a->num_heads * 64, 256);
   return w;
 }
 
@@ -514,39 +547,21 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
     const long long n = (long long)a->total_q * a->num_heads;
     LaunchScope scope(kKBwdPre, s);
     bwd_preprocess_kernel<T, D><<<(unsigned)((n + 7) / 8), 256, 0, s>>>((const T*)a->o, (const T*)a->d_o, a->lse, ld,
+                                                                        (uint4*)(base + ws.fold), 1.f / (a->scale * kLog2e),
                                                                         ws.ld_stride, a->total_q, a->num_heads);
     VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
   }
 
-  // Measured on B200 (uniform 8 x 8192 and the ragged benchmark batch): the 128-wide kernel is the
-  // faster dQ kernel (its dS has spare TMEM columns, so score MMAs overlap the element-wise work),
-  // the 64-wide kernel with double-buffered scores is the faster dK/dV kernel.
+  // both kernels on 128 x 128 tiles (sm100_varlen_bwd128.cu); the 64-row-block template below serves
+  // the absorb operator (D = 256), whose tiles leave no room for 128-row inner blocks
   Bwd128Launch L;
   L.q = a->q; L.k = a->k; L.v = a->v; L.d_o = a->d_o; L.dq = a->dq; L.dk = a->dk; L.dv = a->dv;
-  L.ld = ld; L.ld_stride = ws.ld_stride;
+  L.ld = ld; L.ld_stride = ws.ld_stride; L.aug = base + ws.fold;
   L.hdr_dq = sq.header; L.items_dq = sq.items; L.hdr_dkv = sk.header; L.items_dkv = sk.items;
   L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.D = D; L.dtype = a->dtype; L.sms = sms;
   L.scale = a->scale; L.status = a->status;
-  L.run_dq = 1; L.run_dkv = 0;
-  if ((rc = sm100_varlen_bwd128_launch(L, s))) return rc;
-
-  CUtensorMap k128, v128, q64, do64;
-  if ((rc = encode_tmap_rows(&k128, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&v128, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&q64, a->q, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
-  if ((rc = encode_tmap_rows(&do64, a->d_o, a->dtype, a->total_q, a->num_heads, D, kInner))) return rc;
-  BwdParams p;
-  p.ld = ld; p.ld_stride = ws.ld_stride; p.H = a->num_heads;
-  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e; p.status = a->status;
-  const size_t smem = sizeof(BwdSmem<D>) + 1024;
-  p.out0 = a->dv; p.out1 = a->dk; p.header = sk.header; p.items = sk.items;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    LaunchScope scope(kKBwdDkv, s);
-    varlen_bwd_kernel<T, D, true, false><<<sms, kBwdThreads, smem, s>>>(k128, v128, q64, do64, p);
-  }
-  VAFA_LAUNCH_CHECK("varlen_bwd_kernel<dKV>");
-  return 0;
+  L.run_dq = 1; L.run_dkv = 1;
+  return sm100_varlen_bwd128_launch(L, s);
 }
 
 

@@ -1,18 +1,30 @@
 // Packed variable-length attention backward, 128 x 128 tiles (tcgen05 + TMA + TMEM).
 //
-// Same mathematics and the same two-kernel split as sm100_varlen_bwd.cu (dQ kernel per query tile,
-// dK/dV kernel per key tile, no atomics), but the inner blocks are 128 rows: the score products
-// run as M128 x N128 MMAs, which reach the full tensor rate (N = 64 MMAs measured 56 % of it), and
-// every outer tile is read from shared memory half as often per inner row.
+// Two kernels from one template, no atomics (gradients are run-to-run identical):
+//   dQ    : one 128-row query tile per item (outer = Q, dO), walks the segment's keys (inner = K, V)
+//   dK/dV : one 128-row key tile per item (outer = K, V), walks the segment's query rows (inner = Q, dO)
+// All score products are M128 x N128 MMAs (N = 64 measured 56 % of the tensor rate).
 //
-// TMEM (512 columns): X [0,128) and Y [128,256) fp32 scores (single buffered), ACC0 [256,384),
-// ACC1 [384,512).
-//   dQ : S = Q K^T -> X, dP = dO V^T -> Y; the element-wise warps write the 16-bit dS into one of
-//        two 64-column buffers inside the ACC1 range (unused by dQ), so the next block's S/dP
-//        MMAs are issued as soon as X/Y have been read, and dQ += dS K (from the dS buffer) runs
-//        while the next block's element-wise work does.
-//   dKV: S^T -> X, dP^T -> Y; P^T and dS^T overwrite the first halves of their own source chunks;
-//        dV += P^T dO, dK += dS^T Q use all four regions, so the phases of a block run in sequence.
+// The element-wise work of a block is split in two phases, so that with single score buffers the
+// tensor pipe always has the other phase's product to run:
+//   phase 1:  P  = 2^(c X - lse)          needs X = outerA . innerA^T
+//   phase 2:  dS = P (Y - delta)          needs Y = outerB . innerB^T
+// dK/dV (TMEM: X [0,128) Y [128,256) dV [256,384) dK [384,512)), issue order in steady state
+//     dV += P^T dO(g) ; X(g+1)   |   dK += dS^T Q(g) ; Y(g+1)
+//   P^T overwrites X and dS^T overwrites Y in place (16-bit, packed); the next X is issued behind
+//   the product that reads P^T, the next Y behind the product that reads dS^T (the pipe runs in order).
+// dQ (TMEM: X0 [0,128) X1 [128,256) Y [256,384) dQ [384,512)), steady state
+//     dQ += dS K(g) ; Y(g+1) ; X(g+2)
+//   dS overwrites X[g&1] in place; the scores of block g+1 are already there when phase 1 of g+1 starts.
+//
+// In the dK/dV kernel a thread owns a key row, so lse and delta vary along its columns.  Instead of
+// reading them per element from shared memory (measured: about 1000 cycles per block), they are
+// folded into the score products as one extra K = 16 step:  X' = K Q^T + 1 . L^T with
+// L[q] = split3(-lse[q] / c) in the I/O dtype (three 16-bit pieces carry a 24-bit value, the products
+// with 1 are exact and the sum is accumulated in fp32), likewise Y' = V dO^T - delta.  The pieces are
+// written once per (token, head) by the preprocess kernel and arrive by TMA with the Q block.
+// Then P = 2^(c X') and dS = P Y' need no per-column operand at all.
+//
 // Reference: triton_fa_varlen_v2/triton_fa_varlen_v2/kernels.py:233-350 (dQ), :367-494 (dK/dV).
 #include <cuda.h>
 #include <type_traits>
@@ -36,37 +48,48 @@ using namespace ptx;
 
 constexpr int kThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
 constexpr int kIn = 128;       // rows per inner block
-constexpr int kLdSlots = 132;  // staged (lse, delta) pairs per block: 128 + alignment slack, padded
+constexpr int kAugBytes = 128 * 32;  // one fold tile: 128 rows x 16 elements, 32-byte swizzle
 
-template <int D>
+template <int D, bool kDKV>
 struct Cfg128 {
-  static constexpr int kStages = (D == 128) ? 2 : 4;
+  // ring A holds K (dQ) or Q (dK/dV): live from the score product to the accumulate product of its
+  // block; ring B holds V (dQ: read once) or dO (dK/dV)
+  static constexpr int kSA = kDKV ? (D == 128 ? 2 : 4) : (D == 128 ? 3 : 6);
+  static constexpr int kSB = (D == 128) ? 2 : 4;
   static constexpr int kSub = D / 64;
   static constexpr int kSubBytes = 128 * 128;  // 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;
-  static constexpr uint32_t kX = 0, kY = 128, kAcc0 = 256, kAcc1 = 384;
+  static constexpr uint32_t kX = 0;
+  static constexpr uint32_t kY = kDKV ? 128 : 256;
+  static constexpr uint32_t kAcc0 = kDKV ? 256 : 384;
+  static constexpr uint32_t kAcc1 = 384;  // dK (dK/dV kernel only)
 };
 
-template <int D>
+template <int D, bool kDKV>
 struct Smem128 {
-  alignas(1024) uint8_t outer_a[Cfg128<D>::kTileBytes];
-  alignas(1024) uint8_t outer_b[Cfg128<D>::kTileBytes];
-  alignas(1024) uint8_t inner_a[Cfg128<D>::kStages][Cfg128<D>::kTileBytes];
-  alignas(1024) uint8_t inner_b[Cfg128<D>::kStages][Cfg128<D>::kTileBytes];
+  using Cfg = Cfg128<D, kDKV>;
+  alignas(1024) uint8_t outer_a[Cfg::kTileBytes];
+  alignas(1024) uint8_t outer_b[Cfg::kTileBytes];
+  alignas(1024) uint8_t inner_a[Cfg::kSA][Cfg::kTileBytes];
+  alignas(1024) uint8_t inner_b[Cfg::kSB][Cfg::kTileBytes];
+  alignas(1024) uint8_t aug[kDKV ? Cfg::kSA : 1][2][kDKV ? kAugBytes : 16];  // [slot][lse, delta]
+  alignas(1024) uint8_t ones[kDKV ? kAugBytes : 16];
   alignas(8) uint64_t outer_full, outer_free;
-  uint64_t in_full[Cfg128<D>::kStages], in_empty[Cfg128<D>::kStages];
-  uint64_t xy_full, ds_full, acc_done;
-  alignas(16) float2 ld[Cfg128<D>::kStages][kLdSlots];
+  uint64_t a_full[Cfg::kSA], a_empty[Cfg::kSA];
+  uint64_t b_full[Cfg::kSB], b_empty[Cfg::kSB];
+  uint64_t x_full[2], y_full, p_full, ds_full, acc_done;
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
 };
-static_assert(sizeof(Smem128<128>) + 1024 <= 227 * 1024 && sizeof(Smem128<64>) + 1024 <= 227 * 1024, "shared memory budget");
+static_assert(sizeof(Smem128<128, false>) + 1024 <= 227 * 1024 && sizeof(Smem128<128, true>) + 1024 <= 227 * 1024 &&
+                  sizeof(Smem128<64, false>) + 1024 <= 227 * 1024 && sizeof(Smem128<64, true>) + 1024 <= 227 * 1024,
+              "shared memory budget");
 
 struct Params128 {
   void* out0;        // dQ, or dV
   void* out1;        // unused, or dK
-  const float2* ld;  // [H][ld_stride] (lse, or +inf for rows that saw no key; delta)
+  const float2* ld;  // [H][ld_stride] (lse, or +inf for rows that saw no key; delta): dQ kernel
   long long ld_stride;
   const SchedHeader* header;
   const WorkItem* items;
@@ -77,15 +100,19 @@ struct Params128 {
   long long* trace;
 };
 
+// descriptor high word of the fold tiles: SBO = 256 B (8 rows x 32 B), version 1, SWIZZLE_32B
+constexpr uint32_t kDescHiSw32 = (256u >> 4) | (1u << 14) | (6u << 29);
+
 template <typename T, int D, bool kDKV>
 __global__ void __launch_bounds__(kThreads, 1)
 varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid_constant__ CUtensorMap tmap_outer_b,
                      const __grid_constant__ CUtensorMap tmap_inner_a, const __grid_constant__ CUtensorMap tmap_inner_b,
-                     const Params128 p) {
-  using Cfg = Cfg128<D>;
-  constexpr int S = Cfg::kStages;
+                     const __grid_constant__ CUtensorMap tmap_aug, const Params128 p) {
+  using Cfg = Cfg128<D, kDKV>;
+  constexpr int SA = Cfg::kSA, SB = Cfg::kSB;
   extern __shared__ uint8_t smem_raw[];
-  Smem128<D>& sm = *reinterpret_cast<Smem128<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  using Smem = Smem128<D, kDKV>;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sm.abort_flag;
 
@@ -94,20 +121,36 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
     wq_init(sm.wq, 9);
     mbar_init(smem_u32(&sm.outer_full), 1);
     mbar_init(smem_u32(&sm.outer_free), 1);
-    for (int i = 0; i < S; ++i) {
-      mbar_init(smem_u32(&sm.in_full[i]), 1);
-      mbar_init(smem_u32(&sm.in_empty[i]), 1);
+    for (int i = 0; i < SA; ++i) {
+      mbar_init(smem_u32(&sm.a_full[i]), 1);
+      mbar_init(smem_u32(&sm.a_empty[i]), 1);
     }
-    mbar_init(smem_u32(&sm.xy_full), 1);
-    mbar_init(smem_u32(&sm.ds_full), 256);
+    for (int i = 0; i < SB; ++i) {
+      mbar_init(smem_u32(&sm.b_full[i]), 1);
+      mbar_init(smem_u32(&sm.b_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&sm.x_full[0]), 1);
+    mbar_init(smem_u32(&sm.x_full[1]), 1);
+    mbar_init(smem_u32(&sm.y_full), 1);
+    mbar_init(smem_u32(&sm.p_full), 8);   // one arrival per element-wise warp
+    mbar_init(smem_u32(&sm.ds_full), 8);
     mbar_init(smem_u32(&sm.acc_done), 1);
     fence_barrier_init();
+  }
+  if (kDKV && warp < 8) {
+    // the constant operand of the fold step: every element 1 (bf16) or 64 (fp16, whose pieces are
+    // stored divided by 64 to keep them in range); uniform, so the swizzle does not matter
+    const uint32_t one2 = std::is_same<T, __nv_bfloat16>::value ? 0x3F803F80u : 0x54005400u;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(sm.ones);
+    for (int i = threadIdx.x; i < kAugBytes / 4; i += 256) o32[i] = one2;
+    fence_proxy_async();
   }
   if (warp == 8 && lane == 0) {
     prefetch_tensormap(&tmap_outer_a);
     prefetch_tensormap(&tmap_outer_b);
     prefetch_tensormap(&tmap_inner_a);
     prefetch_tensormap(&tmap_inner_b);
+    if (kDKV) prefetch_tensormap(&tmap_aug);
   }
   if (warp == 9) {
     tmem_alloc(smem_u32(&sm.tmem_base), 512);
@@ -147,21 +190,21 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
           tma_load_3d(smem_u32(sm.outer_b) + c * Cfg::kSubBytes, &tmap_outer_b, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
         }
         for (int b = 0; b < nb; ++b, ++gk) {
-          const int st = gk % S;
-          const uint32_t ph = (gk / S) & 1;
+          const int sa = gk % SA, sb = gk % SB;
           const int row = w.i_start + b * kIn;
-          if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
-          mbar_expect_tx(smem_u32(&sm.in_full[st]), 2 * Cfg::kTileBytes + (kDKV ? 130 * 8 : 0));
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.a_empty[sa]), ((gk / SA) & 1) ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(0); }
+          mbar_expect_tx(smem_u32(&sm.a_full[sa]), Cfg::kTileBytes + (kDKV ? 2 * kAugBytes : 0));
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.inner_a[sa]) + c * Cfg::kSubBytes, &tmap_inner_a, smem_u32(&sm.a_full[sa]), c * 64, h, row);
           if (kDKV) {
-            // (lse, delta) of rows [row, row+128): start at the even index at or below `row` (16-byte
-            // alignment), 130 pairs; readers skip (row & 1) slots
-            const float2* src = p.ld + (long long)h * p.ld_stride + (row & ~1);
-            bulk_load_1d(smem_u32(&sm.ld[st][0]), src, 130 * 8, smem_u32(&sm.in_full[st]));
+            // fold pieces of the block's 128 query rows: elements [0,16) for lse, [16,32) for delta
+            tma_load_3d(smem_u32(sm.aug[sa][0]), &tmap_aug, smem_u32(&sm.a_full[sa]), 0, h, row);
+            tma_load_3d(smem_u32(sm.aug[sa][1]), &tmap_aug, smem_u32(&sm.a_full[sa]), 16, h, row);
           }
-          for (int c = 0; c < Cfg::kSub; ++c) {
-            tma_load_3d(smem_u32(sm.inner_a[st]) + c * Cfg::kSubBytes, &tmap_inner_a, smem_u32(&sm.in_full[st]), c * 64, h, row);
-            tma_load_3d(smem_u32(sm.inner_b[st]) + c * Cfg::kSubBytes, &tmap_inner_b, smem_u32(&sm.in_full[st]), c * 64, h, row);
-          }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.b_empty[sb]), ((gk / SB) & 1) ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
+          mbar_expect_tx(smem_u32(&sm.b_full[sb]), Cfg::kTileBytes);
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.inner_b[sb]) + c * Cfg::kSubBytes, &tmap_inner_b, smem_u32(&sm.b_full[sb]), c * 64, h, row);
         }
         ++qi;
       }
@@ -174,55 +217,54 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
       constexpr uint32_t idesc_acc = make_idesc(kFmt, 0, 1, 128, D);   // A from TMEM, B MN-major
       uint32_t gk = 0, qi = 0;
       bool alive = true;
+      const uint32_t oa_lo = desc_lo_sw128(smem_u32(sm.outer_a), 16), ob_lo = desc_lo_sw128(smem_u32(sm.outer_b), 16);
+      const uint32_t ones_lo = desc_lo_sw128(smem_u32(sm.ones), 16);
 
-      auto issue_xy = [&](uint32_t g, bool last) -> bool {
-        const int st = g % S;
-        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.in_full[st]), (g / S) & 1, abort_flag)) return false; TRACE_ADD(4); }
+      // X(g) = outerA . innerA(g)^T  (+ fold step)
+      auto issue_x = [&](uint32_t g) -> bool {
+        const int sa = g % SA;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.a_full[sa]), (g / SA) & 1, abort_flag)) return false; TRACE_ADD(4); }
         tc_fence_after();
         TRACE_T0();
-        const uint32_t oa_lo = desc_lo_sw128(smem_u32(sm.outer_a), 16), ob_lo = desc_lo_sw128(smem_u32(sm.outer_b), 16);
-        const uint32_t ia_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), 16), ib_lo = desc_lo_sw128(smem_u32(sm.inner_b[st]), 16);
+        const uint32_t x_tmem = tbase + Cfg::kX + (kDKV ? 0u : (g & 1) * 128u);
+        const uint32_t ia_lo = desc_lo_sw128(smem_u32(sm.inner_a[sa]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * (Cfg::kSubBytes >> 4) + (kk & 3) * 2;  // 16-byte units
-          mma_ss2(tbase + Cfg::kX, oa_lo + off, ia_lo + off, idesc_xy, kk > 0);
+          mma_ss2(x_tmem, oa_lo + off, ia_lo + off, idesc_xy, kk > 0);
         }
+        if (kDKV) mma_ss2h(x_tmem, ones_lo, desc_lo_sw128(smem_u32(sm.aug[sa][0]), 16), idesc_xy, 1u, kDescHiSw32);
+        mma_commit(smem_u32(&sm.x_full[kDKV ? 0 : (g & 1)]));
+        TRACE_ADD(14);
+        return true;
+      };
+      // Y(g) = outerB . innerB(g)^T  (+ fold step); the last one of an item releases the outer tiles
+      auto issue_y = [&](uint32_t g, bool last) -> bool {
+        const int sa = g % SA, sb = g % SB;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.b_full[sb]), (g / SB) & 1, abort_flag)) return false; TRACE_ADD(5); }
+        tc_fence_after();
+        TRACE_T0();
+        const uint32_t ib_lo = desc_lo_sw128(smem_u32(sm.inner_b[sb]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * (Cfg::kSubBytes >> 4) + (kk & 3) * 2;
           mma_ss2(tbase + Cfg::kY, ob_lo + off, ib_lo + off, idesc_xy, kk > 0);
         }
-        mma_commit(smem_u32(&sm.xy_full));
+        if (kDKV) mma_ss2h(tbase + Cfg::kY, ones_lo, desc_lo_sw128(smem_u32(sm.aug[sa][1]), 16), idesc_xy, 1u, kDescHiSw32);
+        mma_commit(smem_u32(&sm.y_full));
+        if (!kDKV) mma_commit(smem_u32(&sm.b_empty[sb]));  // V is read by this product only
         if (last) mma_commit(smem_u32(&sm.outer_free));
-        TRACE_ADD(6);
+        TRACE_ADD(14);
         return true;
       };
-      auto issue_acc = [&](uint32_t g, bool first, bool last) {
-        const int st = g % S;
-        const uint32_t acc = first ? 0u : 1u;
+      // ACC (+)= A[TMEM, 16-bit packed: K-step kk at column (kk/2)*32 + (kk%2)*8] . B[shared, MN-major]
+      auto issue_acc = [&](uint32_t d_tmem, uint32_t a_tmem, const uint8_t* b_tile, bool first) {
         TRACE_T0();
-        const uint32_t ma_lo = desc_lo_sw128(smem_u32(sm.inner_a[st]), Cfg::kSubBytes);
-        const uint32_t mb_lo = desc_lo_sw128(smem_u32(sm.inner_b[st]), Cfg::kSubBytes);
-        if (!kDKV) {
-          // dQ += dS . K_g   (dS: 16-bit, contiguous in its buffer; K block MN-major)
-          const uint32_t ds_tmem = tbase + Cfg::kAcc1 + (g & 1) * 64;
+        const uint32_t b_lo = desc_lo_sw128(smem_u32(b_tile), Cfg::kSubBytes);
 #pragma unroll
-          for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts2(tbase + Cfg::kAcc0, ds_tmem + kk * 8, ma_lo + kk * (2048 >> 4), idesc_acc, (acc | (kk > 0)) ? 1u : 0u);
-        } else {
-          // dV += P^T . dO_g ;  dK += dS^T . Q_g   (K-step kk sits at column (kk/2)*32 + (kk%2)*8)
-#pragma unroll
-          for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts2(tbase + Cfg::kAcc0, tbase + Cfg::kX + (kk >> 1) * 32 + (kk & 1) * 8, mb_lo + kk * (2048 >> 4), idesc_acc,
-                    (acc | (kk > 0)) ? 1u : 0u);
-#pragma unroll
-          for (int kk = 0; kk < kIn / 16; ++kk)
-            mma_ts2(tbase + Cfg::kAcc1, tbase + Cfg::kY + (kk >> 1) * 32 + (kk & 1) * 8, ma_lo + kk * (2048 >> 4), idesc_acc,
-                    (acc | (kk > 0)) ? 1u : 0u);
-        }
-        mma_commit(smem_u32(&sm.in_empty[st]));
-        if (last) mma_commit(smem_u32(&sm.acc_done));
-        TRACE_ADD(7);
+        for (int kk = 0; kk < kIn / 16; ++kk)
+          mma_ts2(d_tmem, a_tmem + (kk >> 1) * 32 + (kk & 1) * 8, b_lo + kk * (2048 >> 4), idesc_acc, (!first || kk > 0) ? 1u : 0u);
+        TRACE_ADD(2);
       };
 
       for (uint32_t n = 0; alive; ++n) {
@@ -231,22 +273,39 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         const WorkItem w = p.items[idx];
         const int nb = (w.i_len + kIn - 1) / kIn;
         if (nb == 0) continue;
-        if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
         tc_fence_after();
-        if (!issue_xy(gk, nb == 1)) break;
+        if (!issue_x(gk) || !issue_y(gk, nb == 1)) break;
+        if (!kDKV && nb > 1 && !issue_x(gk + 1)) break;
         for (int b = 0; b < nb; ++b) {
           const uint32_t g = gk + b;
-          // the element-wise warps have read X/Y of block g and written dS (or P^T, dS^T)
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.ds_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(5); }
-          tc_fence_after();
-          if (!kDKV) {
-            // X/Y are free again: next scores first, then this block's dQ product overlaps the
-            // element-wise work on those scores
-            if (b + 1 < nb && !issue_xy(g + 1, b + 2 == nb)) { alive = false; break; }
-            issue_acc(g, b == 0, b + 1 == nb);
+          const int sa = g % SA, sb = g % SB;
+          if (kDKV) {
+            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.p_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
+            tc_fence_after();
+            issue_acc(tbase + Cfg::kAcc0, tbase + Cfg::kX, sm.inner_b[sb], b == 0);  // dV += P^T dO
+            mma_commit(smem_u32(&sm.b_empty[sb]));
+            if (b + 1 < nb && !issue_x(g + 1)) { alive = false; break; }
+            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.ds_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(7); }
+            tc_fence_after();
+            issue_acc(tbase + Cfg::kAcc1, tbase + Cfg::kY, sm.inner_a[sa], b == 0);  // dK += dS^T Q
+            mma_commit(smem_u32(&sm.a_empty[sa]));
+            if (b + 1 < nb) {
+              if (!issue_y(g + 1, b + 2 == nb)) { alive = false; break; }
+            } else {
+              mma_commit(smem_u32(&sm.acc_done));
+            }
           } else {
-            issue_acc(g, b == 0, b + 1 == nb);
-            if (b + 1 < nb && !issue_xy(g + 1, b + 2 == nb)) { alive = false; break; }
+            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.ds_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(7); }
+            tc_fence_after();
+            issue_acc(tbase + Cfg::kAcc0, tbase + Cfg::kX + (g & 1) * 128u, sm.inner_a[sa], b == 0);  // dQ += dS K
+            mma_commit(smem_u32(&sm.a_empty[sa]));
+            if (b + 1 < nb) {
+              if (!issue_y(g + 1, b + 2 == nb)) { alive = false; break; }
+              if (b + 2 < nb && !issue_x(g + 2)) { alive = false; break; }
+            } else {
+              mma_commit(smem_u32(&sm.acc_done));
+            }
           }
         }
         gk += nb;
@@ -270,20 +329,15 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
       const int h = w.head;
       const int nb = (w.i_len + kIn - 1) / kIn;
       const bool row_ok = r < w.o_rows;
-      float my_lse = INFINITY, my_delta = 0.f;
+      float neg_lse = -INFINITY, my_delta = 0.f;
       if (!kDKV && row_ok && nb > 0) {
         const float2 t = p.ld[(long long)h * p.ld_stride + w.o_start + r];
-        my_lse = t.x;
+        neg_lse = -t.x;
         my_delta = t.y;
       }
 
       for (int b = 0; b < nb; ++b) {
         const uint32_t g = gk + b;
-        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.xy_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(8); }
-        tc_fence_after();
-#ifdef VAFA_TRACE
-        const long long t_c0 = clock64();
-#endif
         // visibility of inner index jj = b*128 + col for this thread's outer row r
         //   dQ : jj < i_len and (causal) jj <= r + diag
         //   dKV: jj < i_len and (causal) jj >= r + diag
@@ -293,67 +347,92 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
           else lo = r + w.diag - b * kIn;
         }
         const bool need_mask = (hi < kIn - 1) || (lo > 0);
-        const int st = g % S;
-        const int ld_skip = (w.i_start + b * kIn) & 1;
+        const uint32_t x_addr = lane_base + Cfg::kX + (kDKV ? 0u : (g & 1) * 128u);
+        const uint32_t y_addr = lane_base + Cfg::kY;
+
+        // ---- phase 1: P ----
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.x_full[kDKV ? 0 : (g & 1)]), kDKV ? (g & 1) : ((g >> 1) & 1), abort_flag)) { alive = false; break; } TRACE_ADD(8); }
+        tc_fence_after();
+#ifdef VAFA_TRACE
+        const long long t_p1 = clock64();
+#endif
+        float pf[64];
+        // masked blocks (tails, the causal diagonal) take their own copy of the loop: folded into one
+        // loop the two compares and the select per element ran in every block
+        auto phase1 = [&](auto mask_tag) {
+          constexpr bool kMask = decltype(mask_tag)::value;
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2) {
+            const int chunk = half * 2 + q2;  // 32-column chunk of the block
+            uint32_t xs[32];
+            tmem_ld32(x_addr + chunk * 32, xs);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              // dK/dV: the product already holds S - lse/c
+              float pr = kDKV ? ex2(__uint_as_float(xs[i]) * c) : ex2(fmaf(__uint_as_float(xs[i]), c, neg_lse));
+              if (kMask) {
+                const int col = chunk * 32 + i;
+                pr = ((col >= lo) && (col <= hi)) ? pr : 0.f;
+              }
+              pf[q2 * 32 + i] = pr;
+            }
+            if (kDKV) {
+              // P^T in place: 16 packed columns over the first half of the chunk just read
+              uint32_t pp[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) pp[i] = pack2<T>(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]);
+              tmem_st16(x_addr + chunk * 32, pp);
+            }
+          }
+        };
+        // warp-uniform choice: the TMEM loads and stores inside are .sync.aligned
+        if (__any_sync(0xffffffffu, need_mask)) phase1(std::true_type{}); else phase1(std::false_type{});
         if (kDKV) {
-          // the staged (lse, delta) block arrived with this stage's tiles (complete by now; the wait
-          // orders the reads below after the copy)
-          if (!mbar_wait(smem_u32(&sm.in_full[st]), (g / S) & 1, abort_flag)) { alive = false; break; }
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sm.p_full));
         }
+
+#ifdef VAFA_TRACE
+        tr[12] += clock64() - t_p1;
+#endif
+        // ---- phase 2: dS ----
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.y_full), g & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
+        tc_fence_after();
+#ifdef VAFA_TRACE
+        const long long t_p2 = clock64();
+#endif
 #pragma unroll
         for (int q2 = 0; q2 < 2; ++q2) {
-          const int chunk = half * 2 + q2;  // 32-column chunk of the block
-          uint32_t xs[32], ys[32];
-          tmem_ld32(lane_base + Cfg::kX + chunk * 32, xs);
-          tmem_ld32(lane_base + Cfg::kY + chunk * 32, ys);
+          const int chunk = half * 2 + q2;
+          uint32_t ys[32];
+          tmem_ld32(y_addr + chunk * 32, ys);
           tmem_wait_ld();
-          uint32_t pp[16], dd[16];
+          uint32_t dd[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float pv[2], dv[2];
+            float dv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int col = chunk * 32 + i + e;
-              float lse_v, delta_v;
-#ifdef VAFA_EXP_NOLDS
-              if (false) {
-#else
-              if (kDKV) {
-#endif
-                const float2 t = sm.ld[st][ld_skip + col];
-                lse_v = t.x;
-                delta_v = t.y;
-              } else {
-                lse_v = my_lse;
-                delta_v = my_delta;
-              }
-              float pr = ex2(fmaf(__uint_as_float(xs[i + e]), c, -lse_v));
-              float ds = pr * (__uint_as_float(ys[i + e]) - delta_v);
-              if (need_mask) {
-                const bool vis = (col >= lo) && (col <= hi);
-                pr = vis ? pr : 0.f;
-                ds = vis ? ds : 0.f;
-              }
-              pv[e] = pr;
-              dv[e] = ds;
+              // dK/dV: the product already holds dP - delta
+              const float y = __uint_as_float(ys[i + e]);
+              // masked columns have P = 0 exactly, and the other factor is finite there (rows of a
+              // neighbouring segment, or zero fill past the end of the tensor)
+              dv[e] = pf[q2 * 32 + i + e] * (kDKV ? y : (y - my_delta));
             }
-            pp[i >> 1] = pack2<T>(pv[0], pv[1]);
             dd[i >> 1] = pack2<T>(dv[0], dv[1]);
           }
-          if (!kDKV) {
-            // dS buffer (g & 1) inside the ACC1 range, packed contiguously: chunk -> 16 columns
-            tmem_st16(lane_base + Cfg::kAcc1 + (g & 1) * 64 + chunk * 16, dd);
-          } else {
-            // in place: 16 packed columns over the first half of the chunk just read
-            tmem_st16(lane_base + Cfg::kX + chunk * 32, pp);
-            tmem_st16(lane_base + Cfg::kY + chunk * 32, dd);
-          }
+          // dQ: dS over the scores just consumed (X[g&1]); dK/dV: dS^T over dP^T (Y); in place as above
+          tmem_st16((kDKV ? y_addr : x_addr) + chunk * 32, dd);
         }
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(smem_u32(&sm.ds_full));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.ds_full));
 #ifdef VAFA_TRACE
-        tr[10] += clock64() - t_c0;
+        tr[13] += clock64() - t_p2;
         tr[11] += 1;
 #endif
       }
@@ -362,7 +441,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 
       // ---- epilogue: each half of the warps converts and stores half of the columns ----
       if (nb > 0) {
-        if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break; TRACE_ADD(10); }
         tc_fence_after();
         ++qi;
       }
@@ -440,32 +519,35 @@ static int launch128(const Bwd128Launch& L, cudaStream_t s) {
     vafa_trace_buffer_bwd = g_trace;
   }
 #endif
-  const size_t smem = sizeof(Smem128<D>) + 1024;
-  CUtensorMap q128, do128, k128, v128;
+  CUtensorMap q128, do128, k128, v128, aug;
   int rc;
   if ((rc = encode_tmap_rows(&q128, L.q, L.dtype, L.total_q, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&do128, L.d_o, L.dtype, L.total_q, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&k128, L.k, L.dtype, L.total_k, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&v128, L.v, L.dtype, L.total_k, L.H, D, 128))) return rc;
+  if ((rc = encode_tmap_fold(&aug, L.aug, L.dtype, L.total_q, L.H))) return rc;
   if (L.run_dq) {
-  // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
-  p.out0 = L.dq; p.out1 = nullptr; p.header = (const SchedHeader*)L.hdr_dq; p.items = (const WorkItem*)L.items_dq;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    LaunchScope scope(kKBwdDq, s);
-    varlen_bwd128_kernel<T, D, false><<<L.sms, kThreads, smem, s>>>(q128, do128, k128, v128, p);
+    // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
+    const size_t smem = sizeof(Smem128<D, false>) + 1024;
+    p.out0 = L.dq; p.out1 = nullptr; p.header = (const SchedHeader*)L.hdr_dq; p.items = (const WorkItem*)L.items_dq;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+      LaunchScope scope(kKBwdDq, s);
+      varlen_bwd128_kernel<T, D, false><<<L.sms, kThreads, smem, s>>>(q128, do128, k128, v128, aug, p);
+    }
+    VAFA_LAUNCH_CHECK("varlen_bwd128_kernel<dQ>");
   }
-  VAFA_LAUNCH_CHECK("varlen_bwd128_kernel<dQ>");
+  if (L.run_dkv) {
+    // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
+    const size_t smem = sizeof(Smem128<D, true>) + 1024;
+    p.out0 = L.dv; p.out1 = L.dk; p.header = (const SchedHeader*)L.hdr_dkv; p.items = (const WorkItem*)L.items_dkv;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    {
+      LaunchScope scope(kKBwdDkv, s);
+      varlen_bwd128_kernel<T, D, true><<<L.sms, kThreads, smem, s>>>(k128, v128, q128, do128, aug, p);
+    }
+    VAFA_LAUNCH_CHECK("varlen_bwd128_kernel<dKV>");
   }
-  if (!L.run_dkv) return 0;
-  // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
-  p.out0 = L.dv; p.out1 = L.dk; p.header = (const SchedHeader*)L.hdr_dkv; p.items = (const WorkItem*)L.items_dkv;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
-    LaunchScope scope(kKBwdDkv, s);
-    varlen_bwd128_kernel<T, D, true><<<L.sms, kThreads, smem, s>>>(k128, v128, q128, do128, p);
-  }
-  VAFA_LAUNCH_CHECK("varlen_bwd128_kernel<dKV>");
   return 0;
 }
 

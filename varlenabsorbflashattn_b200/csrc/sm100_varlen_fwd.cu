@@ -45,7 +45,10 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = (D == 128) ? 2 : (D == 64 ? 4 : 2);
+  // two stages: K slot g&1 is free again when S(g) is complete and V slot g&1 when P.V(g) is, so
+  // the producer waits on the very barriers the softmax warps use and the MMA issuer needs only two
+  // tcgen05.commit per block (each commit costs the tensor pipe 40-130 cycles)
+  static constexpr int kStages = 2;
   static constexpr int kSub = D / 64;                 // 64-column (128-byte) sub tiles per row
   static constexpr int kSubBytes = 128 * 128;         // one sub tile: 128 rows x 128 B
   static constexpr int kTileBytes = kSub * kSubBytes;
@@ -61,9 +64,8 @@ struct FwdSmem {
   alignas(1024) uint8_t k[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
   alignas(1024) uint8_t v[kAbsorb ? 1 : FwdCfg<D>::kStages][kAbsorb ? 1024 : FwdCfg<D>::kTileBytes];
   alignas(8) uint64_t q_full, q_free;
-  uint64_t k_full[FwdCfg<D>::kStages], k_empty[FwdCfg<D>::kStages];
-  uint64_t v_full[FwdCfg<D>::kStages], v_empty[FwdCfg<D>::kStages];
-  uint64_t s_full[2], p_full[2], o_done;
+  uint64_t k_full[2], v_full[2];
+  uint64_t s_full[2], p_full[2], o_done[2];  // indexed by block parity; phase = (block / 2) & 1
   uint64_t pair_bar[4];       // the two softmax warps of one TMEM lane quadrant
   float xmax[2][2][128];      // [block parity][half][row] partial row maxima
   float xsum[2][128];         // [half][row] partial row sums at the end of an item
@@ -113,15 +115,13 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(smem_u32(&sm.q_free), 1);
     for (int i = 0; i < S; ++i) {
       mbar_init(smem_u32(&sm.k_full[i]), 1);
-      mbar_init(smem_u32(&sm.k_empty[i]), 1);
       mbar_init(smem_u32(&sm.v_full[i]), 1);
-      mbar_init(smem_u32(&sm.v_empty[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.s_full[i]), 1);
       mbar_init(smem_u32(&sm.p_full[i]), 256);
+      mbar_init(smem_u32(&sm.o_done[i]), 1);
     }
-    mbar_init(smem_u32(&sm.o_done), 1);
     fence_barrier_init();
   }
   if (warp == 8 && lane == 0) {
@@ -168,12 +168,13 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * kTile;
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.k_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
+          // slot free: S(gk-2) complete (absorb: P.X(gk-2) complete, the tile doubles as V)
+          { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.o_done[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
             tma_load_3d(smem_u32(sm.k[st]) + c * Cfg::kSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
           if (!kAbsorb) {
-            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
+            { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
             mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
             for (int c = 0; c < Cfg::kSub; ++c)
               tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
@@ -204,7 +205,6 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           const uint32_t off = (kk >> 2) * kSubStep + (kk & 3) * 2;  // in 16-byte units
           mma_ss2(d_tmem, q_lo + off, k_lo + off, idesc_qk, kk > 0);
         }
-        if (!kAbsorb) mma_commit(smem_u32(&sm.k_empty[st]));  // absorb: the tile is still needed for P.X
         mma_commit(smem_u32(&sm.s_full[g & 1]));
         if (last) mma_commit(smem_u32(&sm.q_free));
         return true;
@@ -236,8 +236,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int kk = 0; kk < kTile / 16; ++kk)
             mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, v_lo + kk * (2048 >> 4), idesc_pv,
                     (b > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.v_empty[st]));
-          mma_commit(smem_u32(&sm.o_done));
+          mma_commit(smem_u32(&sm.o_done[g & 1]));
         }
         gk += nb;
         ++qi;
@@ -338,7 +337,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #ifdef VAFA_TRACE
           tr[10] += clock64() - t_sm0;
 #endif
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done), (g - 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
           tc_fence_after();
           if (__any_sync(0xffffffffu, resc)) {
 #pragma unroll
@@ -366,7 +365,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // ---- epilogue ----
       float l_tot = 0.f;
       if (nb > 0) {
-        if (!mbar_wait(smem_u32(&sm.o_done), (gk - 1) & 1, abort_flag)) break;
+        if (!mbar_wait(smem_u32(&sm.o_done[(gk - 1) & 1]), ((gk - 1) >> 1) & 1, abort_flag)) break;
         tc_fence_after();
         sm.xsum[half][r] = l;
         mbar_arrive(pair_bar);
