@@ -108,6 +108,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 64 consecutive 32-bit columns in one instruction.
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
@@ -242,6 +250,57 @@ __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// ---- packed fp32 pairs (sm_100: one instruction, two lanes of the FMA pipe) -------------------
+__device__ __forceinline__ uint64_t pack_f2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma_f2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul_f2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^t for a pair without the special-function unit (16 results/clk/SM, the limit of the softmax
+// loops): n = round(t) by the magic-number add, f = t - n in [-0.5, 0.5], 2^f by a degree-4
+// polynomial (max relative error 2.7e-6), n added into the exponent field.  t is clamped at -126,
+// so -inf and very negative arguments give about 1e-38 instead of 0.
+__device__ __forceinline__ void ex2_poly2(uint64_t t2, float& r0, float& r1) {
+  float a, b;
+  unpack_f2(t2, a, b);
+  a = fmaxf(a, -126.f);
+  b = fmaxf(b, -126.f);
+  t2 = pack_f2(a, b);
+  const uint64_t magic = pack_f2(12582912.f, 12582912.f);  // 1.5 * 2^23
+  const uint64_t r2 = add_f2(t2, magic);
+  const uint64_t n2 = add_f2(r2, pack_f2(-12582912.f, -12582912.f));
+  const uint64_t f2 = fma_f2(n2, pack_f2(-1.f, -1.f), t2);
+  uint64_t p2 = pack_f2(9.5701014340e-03f, 9.5701014340e-03f);
+  p2 = fma_f2(p2, f2, pack_f2(5.5917860282e-02f, 5.5917860282e-02f));
+  p2 = fma_f2(p2, f2, pack_f2(2.4024744840e-01f, 2.4024744840e-01f));
+  p2 = fma_f2(p2, f2, pack_f2(6.9312181474e-01f, 6.9312181474e-01f));
+  p2 = fma_f2(p2, f2, pack_f2(9.9999926144e-01f, 9.9999926144e-01f));
+  float p0, p1, q0, q1;
+  unpack_f2(p2, p0, p1);
+  unpack_f2(r2, q0, q1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(q0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(q1) << 23));
 }
 
 }  // namespace ptx

@@ -48,6 +48,7 @@ using namespace ptx;
 
 constexpr int kThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
 constexpr int kIn = 128;       // rows per inner block
+constexpr int kPolyPeriod = 4;  // one pair in four computes 2^t by polynomial
 constexpr int kAugBytes = 128 * 32;  // one fold tile: 128 rows x 16 elements, 32-byte swizzle
 
 template <int D, bool kDKV>
@@ -361,28 +362,42 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         // loop the two compares and the select per element ran in every block
         auto phase1 = [&](auto mask_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
+          // this thread's 64 columns [64*half, 64*half + 64) in one load
+          uint32_t xs[64];
+          tmem_ld64(x_addr + half * 64, xs);
+          tmem_wait_ld();
+          // exponent t = c X' (dK/dV: the product already holds S - lse/c) or c S - lse, in pairs; every
+          // kPolyPeriod-th pair takes the polynomial 2^t on the FMA pipe, the others the special-function unit
+          const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(neg_lse, neg_lse);
 #pragma unroll
-          for (int q2 = 0; q2 < 2; ++q2) {
-            const int chunk = half * 2 + q2;  // 32-column chunk of the block
-            uint32_t xs[32];
-            tmem_ld32(x_addr + chunk * 32, xs);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              // dK/dV: the product already holds S - lse/c
-              float pr = kDKV ? ex2(__uint_as_float(xs[i]) * c) : ex2(fmaf(__uint_as_float(xs[i]), c, neg_lse));
-              if (kMask) {
-                const int col = chunk * 32 + i;
-                pr = ((col >= lo) && (col <= hi)) ? pr : 0.f;
-              }
-              pf[q2 * 32 + i] = pr;
+          for (int i = 0; i < 32; ++i) {
+            const uint64_t x2 = pack_f2(__uint_as_float(xs[2 * i]), __uint_as_float(xs[2 * i + 1]));
+            const uint64_t t2 = kDKV ? mul_f2(x2, c2) : fma_f2(x2, c2, nl2);
+            float p0, p1;
+            if (i % kPolyPeriod == kPolyPeriod - 1) {
+              ex2_poly2(t2, p0, p1);
+            } else {
+              float t0, t1;
+              unpack_f2(t2, t0, t1);
+              p0 = ex2(t0);
+              p1 = ex2(t1);
             }
-            if (kDKV) {
-              // P^T in place: 16 packed columns over the first half of the chunk just read
+            if (kMask) {
+              const int col = half * 64 + 2 * i;
+              p0 = ((col >= lo) && (col <= hi)) ? p0 : 0.f;
+              p1 = ((col + 1 >= lo) && (col + 1 <= hi)) ? p1 : 0.f;
+            }
+            pf[2 * i] = p0;
+            pf[2 * i + 1] = p1;
+          }
+          if (kDKV) {
+            // P^T in place: each 32-column chunk becomes 16 packed columns over its own first half
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2) {
               uint32_t pp[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) pp[i] = pack2<T>(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]);
-              tmem_st16(x_addr + chunk * 32, pp);
+              tmem_st16(x_addr + (half * 2 + q2) * 32, pp);
             }
           }
         };
@@ -404,28 +419,27 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 #ifdef VAFA_TRACE
         const long long t_p2 = clock64();
 #endif
-#pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2) {
-          const int chunk = half * 2 + q2;
-          uint32_t ys[32];
-          tmem_ld32(y_addr + chunk * 32, ys);
+        {
+          uint32_t ys[64];
+          const uint64_t nd2 = pack_f2(-my_delta, -my_delta);
+          tmem_ld64(y_addr + half * 64, ys);
           tmem_wait_ld();
-          uint32_t dd[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float dv[2];
+          for (int q2 = 0; q2 < 2; ++q2) {
+            uint32_t dd[16];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              // dK/dV: the product already holds dP - delta
-              const float y = __uint_as_float(ys[i + e]);
-              // masked columns have P = 0 exactly, and the other factor is finite there (rows of a
-              // neighbouring segment, or zero fill past the end of the tensor)
-              dv[e] = pf[q2 * 32 + i + e] * (kDKV ? y : (y - my_delta));
+            for (int i = 0; i < 16; ++i) {
+              // dK/dV: the product already holds dP - delta.  Masked columns have P = 0 exactly, and the
+              // other factor is finite there (rows of a neighbouring segment, or zero fill past the end)
+              uint64_t y2 = pack_f2(__uint_as_float(ys[q2 * 32 + 2 * i]), __uint_as_float(ys[q2 * 32 + 2 * i + 1]));
+              if (!kDKV) y2 = add_f2(y2, nd2);
+              float d0, d1;
+              unpack_f2(mul_f2(pack_f2(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]), y2), d0, d1);
+              dd[i] = pack2<T>(d0, d1);
             }
-            dd[i >> 1] = pack2<T>(dv[0], dv[1]);
+            // dQ: dS over the scores just consumed (X[g&1]); dK/dV: dS^T over dP^T (Y); in place as above
+            tmem_st16((kDKV ? y_addr : x_addr) + (half * 2 + q2) * 32, dd);
           }
-          // dQ: dS over the scores just consumed (X[g&1]); dK/dV: dS^T over dP^T (Y); in place as above
-          tmem_st16((kDKV ? y_addr : x_addr) + chunk * 32, dd);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -449,7 +463,9 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 #pragma unroll
       for (int which = 0; which < (kDKV ? 2 : 1); ++which) {
         T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * D;
-        const float mul = (kDKV && which == 0) ? 1.f : p.scale;  // dV unscaled; dQ and dK scaled
+        // dV unscaled; dQ and dK scaled; dQ rows that saw no key are exact zeros (the polynomial 2^t
+        // leaves about 1e-38 where the special-function unit gives 0)
+        const float mul = (kDKV && which == 0) ? 1.f : ((!kDKV && neg_lse == -INFINITY) ? 0.f : p.scale);
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
 #pragma unroll
         for (int c2 = 0; c2 < D / 64; ++c2) {

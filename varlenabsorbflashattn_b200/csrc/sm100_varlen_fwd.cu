@@ -42,6 +42,7 @@ using namespace ptx;
 
 constexpr int kFwdThreads = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+constexpr int kPolyPeriod = 4;             // one pair of exponentials in four runs as a polynomial on the FMA pipe
 
 template <int D>
 struct FwdCfg {
@@ -119,7 +120,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.s_full[i]), 1);
-      mbar_init(smem_u32(&sm.p_full[i]), 256);
+      mbar_init(smem_u32(&sm.p_full[i]), 8);  // lane 0 of each softmax warp
       mbar_init(smem_u32(&sm.o_done[i]), 1);
     }
     fence_barrier_init();
@@ -277,20 +278,17 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const uint32_t s_addr = lane_base + (g & 1) * 128 + half * 64;
         float s[64];
         {
-          uint32_t t0[32], t1[32];
-          tmem_ld32(s_addr + 0, t0);
-          tmem_ld32(s_addr + 32, t1);
+          uint32_t t0[64];
+          tmem_ld64(s_addr, t0);
           tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            s[i] = __uint_as_float(t0[i]);
-            s[32 + i] = __uint_as_float(t1[i]);
-          }
+          for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(t0[i]);
         }
         // mask: inner index jj = b*128 + col is visible iff jj < i_len and (causal) jj <= r + diag
         const int lim_tail = w.i_len - 1 - b * kTile;
         const int lim_diag = w.masked ? (w.diag - b * kTile) : 0x3fffffff;  // for row 0
-        if (lim_tail < kTile - 1 || lim_diag < kTile - 1) {
+        const bool masked_block = lim_tail < kTile - 1 || lim_diag < kTile - 1;  // same for the whole CTA
+        if (masked_block) {
           const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff) - half * 64;
 #pragma unroll
           for (int i = 0; i < 64; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
@@ -319,27 +317,51 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (!resc) m_new = m_ref;
         const float alpha = resc ? ex2(m_ref - m_new) : 1.f;
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // exponents and row sums in packed pairs (one FMA-pipe instruction for two values); in unmasked
+        // blocks every kPolyPeriod-th pair takes the polynomial 2^t instead of the special-function unit
+        // (16 results/clk/SM).  Masked blocks keep the unit for all: it returns exactly 0 for -inf, which
+        // the dead-row test (row sum == 0) relies on.
+        const uint64_t cs2 = pack_f2(c, c), nm2 = pack_f2(-m_use, -m_use);
+        uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
         uint32_t pk[32];
+        auto exps = [&](auto poly_tag) {
+          constexpr bool kPoly = decltype(poly_tag)::value;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2(fmaf(s[2 * i], c, -m_use));
-          const float p1 = ex2(fmaf(s[2 * i + 1], c, -m_use));
-          sum4[i & 3] += p0 + p1;
-          pk[i] = pack2<T>(p0, p1);
+          for (int i = 0; i < 32; ++i) {
+            const uint64_t t2 = fma_f2(pack_f2(s[2 * i], s[2 * i + 1]), cs2, nm2);
+            float p0, p1;
+            if (kPoly && (i % kPolyPeriod == kPolyPeriod - 1)) {
+              ex2_poly2(t2, p0, p1);
+            } else {
+              float t0, t1;
+              unpack_f2(t2, t0, t1);
+              p0 = ex2(t0);
+              p1 = ex2(t1);
+            }
+            sum2[i & 3] = add_f2(sum2[i & 3], pack_f2(p0, p1));
+            pk[i] = pack2<T>(p0, p1);
+          }
+        };
+        if (masked_block) exps(std::false_type{}); else exps(std::true_type{});
+        {
+          float a0, a1, b0, b1;
+          unpack_f2(add_f2(sum2[0], sum2[1]), a0, a1);
+          unpack_f2(add_f2(sum2[2], sum2[3]), b0, b1);
+          l = l * alpha + ((a0 + a1) + (b0 + b1));
         }
-        l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_ref = m_new;
         // 64 probabilities -> 32 packed columns over the first half of the columns just read; the MMA
         // issuer addresses K-step kk at column (kk/4)*64 + (kk%4)*8
         tmem_st32(s_addr, pk);
-        if (b > 0) {
+        if (b > 0 && __any_sync(0xffffffffu, resc)) {
 #ifdef VAFA_TRACE
           tr[10] += clock64() - t_sm0;
 #endif
+          // O may be rescaled once P.V of the previous block is complete (the next one waits for this
+          // warp's arrival below).  No alias in the parity wait: S(g) complete implies P.V(g-2) complete.
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
           tc_fence_after();
-          if (__any_sync(0xffffffffu, resc)) {
+          {
 #pragma unroll
             for (int c2 = 0; c2 < D / 64; ++c2) {
               const int cc = half * (D / 64) + c2;
@@ -354,7 +376,8 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         }
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(smem_u32(&sm.p_full[g & 1]));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.p_full[g & 1]));
 #ifdef VAFA_TRACE
         tr[11] += 1;
 #endif
