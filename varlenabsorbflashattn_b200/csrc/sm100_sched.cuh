@@ -93,5 +93,7 @@ static inline SchedCaps sched_caps(int mode, int total_outer, int total_inner, i
 }
 
 int launch_scheduler(const SchedParams& p, cudaStream_t s);
+// two independent tile lists in one launch (one CTA each)
+int launch_scheduler_pair(const SchedParams& a, const SchedParams& b, cudaStream_t s);
 
 }  // namespace vafa

@@ -1,0 +1,288 @@
+// Body of the single-CTA tile-list builder (see sm100_sched.cuh), as a device function so that it can
+// run as CTAs of another kernel's grid as well.  One call = one CTA of kSchedThreads threads.
+//
+// Order of the emitted work items: segments by descending total cost (bucket sort on a
+// logarithmic scale); inside a segment all heads; inside a head the tiles by descending cost and
+// their splits.  Persistent CTAs take consecutive items, so the CTAs that run at the same time
+// work on tiles of the same (segment, head) and find each other's K/V (or Q/dO) blocks in L2
+// instead of each streaming them from HBM, while the large-to-small order keeps the tail short.
+#pragma once
+#include "sm100_sched.cuh"
+
+namespace vafa {
+namespace sched_impl {
+
+
+constexpr int kSchedThreads = 1024;
+constexpr int kBuckets = 512;
+
+struct Seg {
+  int q0, Lq, k0, Lk, off;
+  int n_tiles;  // outer tiles of the segment
+};
+
+struct Unit {
+  int o_start, o_rows, i_start, i_len, diag;
+};
+
+__device__ __forceinline__ int n_blocks(int len) { return (len + kTile - 1) / kTile; }
+
+__device__ __forceinline__ Seg load_seg(const SchedParams& p, int s) {
+  Seg g;
+  g.q0 = p.cu_q[s]; g.Lq = p.cu_q[s + 1] - g.q0;
+  g.k0 = p.cu_k[s]; g.Lk = p.cu_k[s + 1] - g.k0;
+  g.off = g.Lk - g.Lq;
+  g.n_tiles = (p.mode == kSchedDkv) ? (g.Lk + kTile - 1) / kTile : (g.Lq + p.tile_rows - 1) / p.tile_rows;
+  return g;
+}
+
+// Tile t of a segment, t counted in order of descending cost.
+__device__ __forceinline__ Unit make_unit(const SchedParams& p, const Seg& g, int t) {
+  Unit u;
+  if (p.mode == kSchedDkv) {
+    // key tiles; under the causal mask the first tiles see the most query rows
+    const int j0 = t * kTile;
+    u.o_start = g.k0 + j0;
+    u.o_rows = min(kTile, g.Lk - j0);
+    const int ibeg = p.causal ? max(0, j0 - g.off) : 0;
+    u.i_len = max(0, g.Lq - ibeg);
+    u.i_start = g.q0 + ibeg;
+    u.diag = j0 - g.off - ibeg;  // key row r of the tile and inner row ii: visible iff ii >= r + diag
+  } else {
+    // query tiles; under the causal mask the last tiles see the most keys
+    const int i0 = (p.causal ? (g.n_tiles - 1 - t) : t) * p.tile_rows;
+    u.o_start = g.q0 + i0;
+    u.o_rows = min(p.tile_rows, g.Lq - i0);
+    const int kend = p.causal ? min(g.Lk, i0 + u.o_rows + g.off) : g.Lk;
+    u.i_len = max(0, kend);
+    u.i_start = g.k0;
+    u.diag = i0 + g.off;         // query row r of the tile sees inner row jj iff jj <= r + diag
+  }
+  return u;
+}
+
+__device__ __forceinline__ int n_splits(int nb, int bs) { return (bs > 0 && nb > bs) ? (nb + bs - 1) / bs : 1; }
+
+// Monotone map of a cost to one of kBuckets buckets: 16 buckets per power of two.
+__device__ __forceinline__ int cost_bucket(long long c) {
+  if (c <= 0) return 0;
+  if (c < 16) return (int)c;
+  const int lz = __clzll(c);
+  const int e = 63 - lz;                                  // floor(log2 c) >= 4
+  const int m = (int)((c >> (e - 4)) & 15);               // next four bits
+  return min(kBuckets - 1, 16 * (e - 3) + m);
+}
+
+
+__device__ __forceinline__ void sched_build(const SchedParams& p) {
+  __shared__ int s_hist[kBuckets];
+  __shared__ int s_units, s_items, s_rows, s_bs, s_combine;
+  __shared__ long long s_blocks;
+
+  if (threadIdx.x == 0) { s_units = 0; s_blocks = 0; s_combine = 0; }
+  for (int b = threadIdx.x; b < kBuckets; b += kSchedThreads) s_hist[b] = 0;
+  __syncthreads();
+
+  // Every pass: one warp per segment, lanes over the segment's tiles.
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  constexpr int kWarps = kSchedThreads / 32;
+
+  // pass 1: totals
+  {
+    int units = 0;
+    long long blocks = 0;
+    for (int s = wid; s < p.n_seg; s += kWarps) {
+      const Seg g = load_seg(p, s);
+      for (int t = lane; t < g.n_tiles; t += 32) {
+        const Unit u = make_unit(p, g, t);
+        if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
+      }
+    }
+    if (units) { atomicAdd(&s_units, units); atomicAdd((unsigned long long*)&s_blocks, (unsigned long long)blocks); }
+  }
+  __syncthreads();
+
+  // split policy (forward only): inner blocks per item
+  if (threadIdx.x == 0) {
+    int bs = 0;  // 0 = never split
+    if (p.mode == kSchedFwd) {
+      if (p.split_len > 0) {
+        bs = p.split_len / kTile;
+      } else {
+        const long long par = (long long)s_units * p.H;
+        if (par > 0 && par < 2LL * p.sm_count) {
+          const long long t = (s_blocks * p.H + 2LL * p.sm_count - 1) / (2LL * p.sm_count);
+          bs = (int)max(8LL, t);
+        }
+      }
+    }
+    s_bs = bs;
+  }
+  __syncthreads();
+
+  // pass 2: make the split fit the capacities (double the slice until it does)
+  for (int round = 0; round < 24; ++round) {
+    if (threadIdx.x == 0) { s_items = 0; s_rows = 0; }
+    __syncthreads();
+    const int bs = s_bs;
+    int items = 0, rows = 0;
+    for (int s = wid; s < p.n_seg; s += kWarps) {
+      const Seg g = load_seg(p, s);
+      for (int t = lane; t < g.n_tiles; t += 32) {
+        const Unit u = make_unit(p, g, t);
+        const int ns = n_splits(n_blocks(u.i_len), bs);
+        items += ns;
+        if (ns > 1) rows += ns * u.o_rows;
+      }
+    }
+    if (items) atomicAdd(&s_items, items);
+    if (rows) atomicAdd(&s_rows, rows);
+    __syncthreads();
+    const bool fits = ((long long)s_items * p.H <= p.cap_items) && (s_rows <= p.cap_rows);
+    __syncthreads();
+    if (fits || s_bs == 0) break;
+    if (threadIdx.x == 0) s_bs = (s_bs >= (1 << 24)) ? 0 : s_bs * 2;
+    __syncthreads();
+  }
+  const int bs = s_bs;
+
+  // pass 3: items per cost bucket of their segment
+  for (int s = wid; s < p.n_seg; s += kWarps) {
+    const Seg g = load_seg(p, s);
+    long long cost = 0;
+    int items = 0;
+    for (int t = lane; t < g.n_tiles; t += 32) {
+      const Unit u = make_unit(p, g, t);
+      const int nb = n_blocks(u.i_len);
+      cost += nb;
+      items += n_splits(nb, bs);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      cost += __shfl_xor_sync(0xffffffffu, cost, o);
+      items += __shfl_xor_sync(0xffffffffu, items, o);
+    }
+    if (lane == 0 && items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+  }
+  __syncthreads();
+  // descending exclusive scan: a bucket starts after all buckets of larger cost
+  if (wid == 0) {
+    // lane j owns buckets [kBuckets - 16 (j+1), kBuckets - 16 j), walked downwards
+    constexpr int kPer = kBuckets / 32;
+    const int top = kBuckets - 1 - lane * kPer;
+    int cnt[kPer], sum = 0;
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) { cnt[i] = s_hist[top - i]; sum += cnt[i]; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    int run = incl - sum;  // items in all buckets of larger cost
+#pragma unroll
+    for (int i = 0; i < kPer; ++i) { s_hist[top - i] = run; run += cnt[i]; }
+    if (lane == 31) { s_items = run; s_rows = 0; }
+  }
+  __syncthreads();
+  const bool overflow = s_items > p.cap_items;
+
+  // pass 4: emit, one contiguous range per segment; one warp per segment, lanes over (head, tile)
+  if (!overflow) {
+    for (int s = wid; s < p.n_seg; s += kWarps) {
+      const Seg g = load_seg(p, s);
+      int items = 0, pos = 0, n_split_tiles = 0, c0 = 0;
+      long long cost = 0;
+      for (int t = lane; t < g.n_tiles; t += 32) {
+        const int nb = n_blocks(make_unit(p, g, t).i_len);
+        const int ns = n_splits(nb, bs);
+        cost += nb;
+        items += ns;
+        n_split_tiles += (ns > 1);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        cost += __shfl_xor_sync(0xffffffffu, cost, o);
+        items += __shfl_xor_sync(0xffffffffu, items, o);
+        n_split_tiles += __shfl_xor_sync(0xffffffffu, n_split_tiles, o);
+      }
+      if (lane == 0) {
+        if (items) pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+        if (n_split_tiles) {
+          // split-K bookkeeping once per tile: the partial rows are shared by the heads ([row][head])
+          c0 = atomicAdd(&s_combine, n_split_tiles);
+          int k = 0;
+          for (int t = 0; t < g.n_tiles; ++t) {
+            const Unit u = make_unit(p, g, t);
+            const int ns = n_splits(n_blocks(u.i_len), bs);
+            if (ns > 1) {
+              CombineUnit cu;
+              cu.q_start = u.o_start; cu.q_rows = u.o_rows; cu.n_splits = ns;
+              cu.base = atomicAdd(&s_rows, ns * u.o_rows);
+              p.combine[c0 + k++] = cu;
+            }
+          }
+        }
+      }
+      items = __shfl_sync(0xffffffffu, items, 0);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      n_split_tiles = __shfl_sync(0xffffffffu, n_split_tiles, 0);
+      c0 = __shfl_sync(0xffffffffu, c0, 0);
+      __syncwarp();
+      if (items == 0) continue;
+      if (n_split_tiles == 0) {
+        // one item per tile: position is direct
+        // lanes over tiles (the unit is computed once), then one store per head
+        for (int t = lane; t < g.n_tiles; t += 32) {
+          const Unit u = make_unit(p, g, t);
+          WorkItem w;
+          w.o_start = u.o_start; w.o_rows = u.o_rows; w.i_start = u.i_start; w.i_len = u.i_len;
+          w.diag = u.diag; w.masked = p.causal; w.partial = -1;
+          for (int h = 0; h < p.H; ++h) {
+            w.head = h;
+            p.items[pos + h * items + t] = w;
+          }
+        }
+      } else {
+        for (int h = lane; h < p.H; h += 32) {
+          int at = pos + h * items, k = 0;
+          for (int t = 0; t < g.n_tiles; ++t) {
+            const Unit u = make_unit(p, g, t);
+            const int nb = n_blocks(u.i_len);
+            const int ns = n_splits(nb, bs);
+            const int per = (ns > 1) ? (nb + ns - 1) / ns : nb;
+            const int base = (ns > 1) ? p.combine[c0 + k++].base : -1;
+            for (int sp = 0; sp < ns; ++sp) {
+              const int b0 = sp * per;
+              WorkItem w;
+              w.o_start = u.o_start;
+              w.o_rows = u.o_rows;
+              w.i_start = u.i_start + b0 * kTile;
+              w.i_len = max(0, min(u.i_len - b0 * kTile, per * kTile));
+              w.diag = u.diag - b0 * kTile;
+              w.masked = p.causal;
+              w.partial = (ns > 1) ? base + sp * u.o_rows : -1;
+              w.head = h;
+              p.items[at++] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SchedHeader h;
+    h.n_items = overflow ? -1 : s_items;
+    h.n_combine = s_combine;
+    h.n_partial_rows = s_rows;
+    h.block_len = bs;
+    h.reserved0 = 0;
+    h.next_item = 0;
+    h.pad[0] = h.pad[1] = 0;
+    *p.header = h;
+  }
+}
+
+}  // namespace sched_impl
+}  // namespace vafa

@@ -26,6 +26,7 @@
 
 #include "sm100_common.cuh"
 #include "sm100_kernels.cuh"
+#include "sm100_sched_body.cuh"
 #include "profile.cuh"
 
 namespace vafa {
@@ -449,45 +450,59 @@ __device__ __forceinline__ uint2 fold_pieces(float a) {
 
 // delta = rowsum(O * dO); LD[h][t] = (lse or +inf for rows that saw no key, delta); and the same two
 // numbers as fold rows fold[t][h][0:16] = pieces(-lse / c), fold[t][h][16:32] = pieces(-delta).
+// The first two CTAs of the grid build the tile lists of the dQ and dK/dV kernels instead (they depend
+// on cu_seqlens only): the list builder is latency-bound on one SM and hides under the row pass.
 template <typename T, int D>
-__global__ void __launch_bounds__(256) bwd_preprocess_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
-                                                             const float* __restrict__ lse, float2* __restrict__ ld,
-                                                             uint4* __restrict__ fold, float inv_c,
-                                                             long long ld_stride, int total_q, int H) {
-  const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (w >= (long long)total_q * H) return;
-  const int t = (int)(w / H), h = (int)(w % H);
-  constexpr int V = D / 32;  // elements per lane: 4 or 2
-  const T* a = o + w * D + lane * V;
-  const T* b = d_o + w * D + lane * V;
-  float part = 0.f;
-  if (V == 4) {
-    const uint2 ua = *reinterpret_cast<const uint2*>(a);
-    const uint2 ub = *reinterpret_cast<const uint2*>(b);
-    const T* pa = reinterpret_cast<const T*>(&ua);
-    const T* pb = reinterpret_cast<const T*>(&ub);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) part += to_float(pa[i]) * to_float(pb[i]);
-  } else {
-    const uint32_t ua = *reinterpret_cast<const uint32_t*>(a);
-    const uint32_t ub = *reinterpret_cast<const uint32_t*>(b);
-    const T* pa = reinterpret_cast<const T*>(&ua);
-    const T* pb = reinterpret_cast<const T*>(&ub);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+__global__ void __launch_bounds__(sched_impl::kSchedThreads) bwd_prepare_kernel(
+    const SchedParams sched_dq, const SchedParams sched_dkv, const T* __restrict__ o, const T* __restrict__ d_o,
+    const float* __restrict__ lse, float2* __restrict__ ld, uint4* __restrict__ fold, float inv_c, long long ld_stride,
+    int total_q, int H) {
+  if (blockIdx.x < 2) {
+    sched_impl::sched_build(blockIdx.x == 0 ? sched_dq : sched_dkv);
+    return;
   }
-  part = warp_sum(part);
-  if (lane == 0) {
-    const float l = lse[w];
-    ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
-    const uint2 fl = fold_pieces<T>(l == -INFINITY ? -INFINITY : -l * inv_c);
-    const uint2 fd = fold_pieces<T>(-part);
-    uint4* dst = fold + w * 4;  // 32 elements = 64 B per (token, head)
-    dst[0] = make_uint4(fl.x, fl.y, 0u, 0u);
-    dst[1] = make_uint4(0u, 0u, 0u, 0u);
-    dst[2] = make_uint4(fd.x, fd.y, 0u, 0u);
-    dst[3] = make_uint4(0u, 0u, 0u, 0u);
+  // D/8 lanes per (token, head) row, 16 bytes each; a warp takes 32/(D/8) rows per step and four steps,
+  // with all eight loads of a thread in flight before the first is used
+  constexpr int kLanes = D / 8, kRowsPerStep = 32 / kLanes, kSteps = 4;
+  const int lane = threadIdx.x & 31, sub = lane / kLanes, li = lane % kLanes;
+  const long long n_rows = (long long)total_q * H;
+  constexpr int kWarpsPerCta = sched_impl::kSchedThreads / 32;
+  const long long row0 = ((long long)(blockIdx.x - 2) * kWarpsPerCta + (threadIdx.x >> 5)) * (kRowsPerStep * kSteps) + sub;
+  uint4 a[kSteps], b[kSteps];
+#pragma unroll
+  for (int st = 0; st < kSteps; ++st) {
+    const long long row = row0 + st * kRowsPerStep;
+    a[st] = b[st] = make_uint4(0u, 0u, 0u, 0u);
+    if (row < n_rows) {
+      a[st] = reinterpret_cast<const uint4*>(o + row * D)[li];
+      b[st] = reinterpret_cast<const uint4*>(d_o + row * D)[li];
+    }
+  }
+#pragma unroll
+  for (int st = 0; st < kSteps; ++st) {
+    const long long row = row0 + st * kRowsPerStep;
+    const T* pa = reinterpret_cast<const T*>(&a[st]);
+    const T* pb = reinterpret_cast<const T*>(&b[st]);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+#pragma unroll
+    for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    if (row < n_rows && li < 4) {
+      const int t = (int)(row / H), h = (int)(row % H);
+      const float l = lse[row];
+      if (li == 0) ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
+      // fold row: 32 elements = 64 B = four 16-byte pieces, one per lane
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (li == 0) {
+        const uint2 fl = fold_pieces<T>(l == -INFINITY ? -INFINITY : -l * inv_c);
+        v.x = fl.x; v.y = fl.y;
+      } else if (li == 2) {
+        const uint2 fd = fold_pieces<T>(-part);
+        v.x = fd.x; v.y = fd.y;
+      }
+      fold[row * 4 + li] = v;
+    }
   }
 }
 
@@ -525,7 +540,6 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   const int sms = resolve_sm_count_bwd(a->sm_count);
   const BwdWorkspace ws = bwd_workspace(a, sms);
   char* base = (char*)a->workspace;
-  int rc;
 
   SchedParams sq;
   sq.cu_q = a->cu_seqlens_q; sq.cu_k = a->cu_seqlens_k; sq.n_seg = a->n_seg; sq.mode = kSchedDq;
@@ -534,22 +548,22 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   sq.header = (SchedHeader*)(base + ws.hdr_dq);
   sq.items = (WorkItem*)(base + ws.items_dq);
   sq.combine = nullptr;
-  if ((rc = launch_scheduler(sq, s))) return rc;
   SchedParams sk = sq;
   sk.mode = kSchedDkv;
   sk.cap_items = ws.caps_dkv.cap_items;
   sk.header = (SchedHeader*)(base + ws.hdr_dkv);
   sk.items = (WorkItem*)(base + ws.items_dkv);
-  if ((rc = launch_scheduler(sk, s))) return rc;
 
   float2* ld = (float2*)(base + ws.ld);
   {
     const long long n = (long long)a->total_q * a->num_heads;
+    constexpr int kRowsPerCta = (32 / (D / 8)) * 4 * (sched_impl::kSchedThreads / 32);
+    const unsigned grid = 2u + (unsigned)((n + kRowsPerCta - 1) / kRowsPerCta);
     LaunchScope scope(kKBwdPre, s);
-    bwd_preprocess_kernel<T, D><<<(unsigned)((n + 7) / 8), 256, 0, s>>>((const T*)a->o, (const T*)a->d_o, a->lse, ld,
-                                                                        (uint4*)(base + ws.fold), 1.f / (a->scale * kLog2e),
-                                                                        ws.ld_stride, a->total_q, a->num_heads);
-    VAFA_LAUNCH_CHECK("bwd_preprocess_kernel");
+    bwd_prepare_kernel<T, D><<<grid, sched_impl::kSchedThreads, 0, s>>>(
+        sq, sk, (const T*)a->o, (const T*)a->d_o, a->lse, ld, (uint4*)(base + ws.fold), 1.f / (a->scale * kLog2e),
+        ws.ld_stride, a->total_q, a->num_heads);
+    VAFA_LAUNCH_CHECK("bwd_prepare_kernel");
   }
 
   // both kernels on 128 x 128 tiles (sm100_varlen_bwd128.cu); the 64-row-block template below serves
@@ -624,11 +638,10 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   sq.sm_count = sms; sq.split_len = 0; sq.tile_rows = kTile / a.H;
   sq.cap_items = ws.cap_du; sq.cap_combine = 0; sq.cap_rows = 0;
   sq.header = (SchedHeader*)(base + ws.hdr_du); sq.items = (WorkItem*)(base + ws.items_du); sq.combine = nullptr;
-  if ((rc = launch_scheduler(sq, s))) return rc;
   SchedParams sk = sq;
   sk.mode = kSchedDkv; sk.tile_rows = kTile; sk.cap_items = ws.cap_dx;
   sk.header = (SchedHeader*)(base + ws.hdr_dx); sk.items = (WorkItem*)(base + ws.items_dx);
-  if ((rc = launch_scheduler(sk, s))) return rc;
+  if ((rc = launch_scheduler_pair(sq, sk, s))) return rc;
 
   CUtensorMap u128, g128, x64, x128, u64, g64;
   if ((rc = encode_tmap_rows(&u128, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
