@@ -41,10 +41,10 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # from the ncu capture summarised under profiles/ for the same kernel, or None when no capture
 # exists for this workload.
 NCU_TRAFFIC_BYTES = {
-    # profiles/varlen_kernels_C2_ncu_full.md
-    ("C2", "varlen_bwd_kernel<dKV>"): 533_313_024 + 223_805_184,
-    ("C2", "varlen_bwd_kernel<dQ>"): 539_879_168 + 113_630_720,
-    ("C2", "varlen_fwd_kernel"): 399_230_208 + 110_971_904,
+    # profiles/varlen_kernels_C2_ncu_full.md (dram__bytes_read.sum + dram__bytes_write.sum, one launch)
+    ("C2", "varlen_bwd_kernel<dKV>"): 570_584_832 + 227_940_864,
+    ("C2", "varlen_bwd_kernel<dQ>"): 539_180_544 + 112_521_728,
+    ("C2", "varlen_fwd_kernel"): 399_229_696 + 110_594_816,
 }
 
 
