@@ -180,6 +180,32 @@ def test_ragged_random_causal_fwd_bwd(impl, seed):
     _compare(ins, o, lse, grads, torch.bfloat16, True)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("gain", [1.0, 6.0])
+def test_backward_large_scores_and_dead_rows(dtype, gain):
+    """The dK/dV kernel receives lse and delta as sums of three 16-bit pieces inside its score products:
+    large |lse| (q scaled up, so that |scale * s| reaches several hundred) must not cost accuracy, and
+    query rows that see no key (causal, more queries than keys) must leave dQ exactly zero and add
+    nothing to dK/dV."""
+    V.set_impl("tcgen05")
+    try:
+        ql, kl = [300, 200, 140, 129], [300, 70, 140, 640]
+        q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 2, 128, dtype, 5)
+        q = (q.float() * gain).to(dtype)
+        for causal in (False, True):
+            qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+            o, lse = vb.packed_varlen_attn_with_lse(qg, kg, vg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
+            o.backward(do.to(DEV))
+            _compare((q, k, v, do, cu_q, cu_k), o, lse, (qg.grad, kg.grad, vg.grad), dtype, causal)
+            if causal:
+                # segment 1 has 200 queries over 70 keys: its first 130 rows see nothing
+                dead = qg.grad[300:430]
+                assert torch.count_nonzero(dead).item() == 0
+                assert torch.isinf(lse[300:430]).all()
+    finally:
+        V.set_impl("auto")
+
+
 def test_sequence_sharding_is_bitwise_equivalent():
     """Running each rank's shard of a packed batch on its own gives, row for row, the bits of the
     full-batch run (no sequence crosses ranks and no result depends on its neighbours)."""
