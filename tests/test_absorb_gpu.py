@@ -65,6 +65,23 @@ def test_reference_cases_bf16(name):
     _compare(ins, O, grads, torch.bfloat16)
 
 
+def test_production_dims_run_on_the_tensor_core_kernels():
+    """d_q = 968, d_kv = 216 (the reference's production shape) are zero-padded to 1024 / 256 on the way
+    in, so forward and backward run on the tcgen05 kernels and not on the SIMT attention kernels."""
+    from varlenabsorbflashattn_b200 import _lib
+    ql = uniform_lengths(24, 1, 16, 3)
+    kl = log_uniform_lengths(24, 8, 700, 4)
+    _lib.profile_reset()
+    ins, O, grads = _run(ql, kl, 968, 216, 8, 32, torch.bfloat16, 1)
+    launched = {name for name, v in _lib.profile_read().items() if v[2] > 0}
+    assert {"varlen_fwd_kernel<absorb>", "varlen_bwd_kernel<absorb dU>", "varlen_bwd_kernel<absorb dX>",
+            "gemm_nn_k256_kernel", "gemm_tn_kernel"} <= launched, launched
+    assert not ({"simt_fwd_kernel", "simt_dq_kernel", "simt_dkv_kernel"} & launched), launched
+    assert grads[0].shape == (sum(ql), 968) and grads[1].shape == (sum(kl), 216)
+    assert grads[2].shape == (968, 8, 32) and grads[3].shape == (216, 8, 32) and grads[4].shape == (216, 8, 32)
+    _compare(ins, O, grads, torch.bfloat16)
+
+
 def test_benchmark_dims_bf16():
     """d_q = d_kv = 256, H = 8, D_H = 32 with the benchmark's value distributions
     (q_raw, X ~ N(0,1); W ~ N(0, 1/256)), a scaled-down draw of configuration 4."""

@@ -91,3 +91,25 @@ def test_prepare_indices_format():
     qi, ki = vb.prepare_target_attn_indices(torch.tensor([0, 17, 17, 20]), torch.tensor([0, 130, 131, 131]))
     assert qi.dtype == torch.int32 and qi.tolist() == [[0, 0], [0, 1], [2, 0]]
     assert ki.tolist() == [[0, 0], [0, 1], [0, 2], [1, 0]]
+
+
+def test_absorb_padding_of_production_widths():
+    """The host layer pads d_q = 968 / d_kv = 216 (the reference's production shape) to 1024 / 256 for
+    the tensor-core kernels, with zero columns / rows and differentiable ops; other cases stay as given."""
+    import torch
+    from varlenabsorbflashattn_b200.absorb import _padded_widths, _pad_first, _pad_last
+    assert _padded_widths(torch.bfloat16, 968, 216, 8) == (1024, 256)
+    assert _padded_widths(torch.float16, 256, 216, 8) == (256, 256)
+    assert _padded_widths(torch.bfloat16, 100, 256, 4) == (256, 256)
+    assert _padded_widths(torch.bfloat16, None, 216, 8) == (None, 256)
+    assert _padded_widths(torch.bfloat16, 256, 256, 8) is None      # already fits
+    assert _padded_widths(torch.float32, 968, 216, 8) is None        # fp32 runs on the SIMT kernels
+    assert _padded_widths(torch.bfloat16, 968, 216, 6) is None       # 6 heads do not stack into 128 rows
+    assert _padded_widths(torch.bfloat16, 968, 300, 8) is None       # wider than one tile
+    W = torch.randn(5, 2, 3, requires_grad=True)
+    X = torch.randn(4, 5, requires_grad=True)
+    Wp, Xp = _pad_first(W, 8), _pad_last(X, 8)
+    assert Wp.shape == (8, 2, 3) and Xp.shape == (4, 8)
+    assert torch.equal(Wp[:5], W) and Wp[5:].abs().sum() == 0 and Xp[:, 5:].abs().sum() == 0
+    (Wp.sum() * 2 + Xp.sum() * 3).backward()
+    assert W.grad.shape == W.shape and torch.all(W.grad == 2) and torch.all(X.grad == 3)

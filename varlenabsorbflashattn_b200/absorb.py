@@ -13,7 +13,12 @@ Differences that stay behind the same signature:
     the device from cu_seqlens;
   * `weight_grad_group` (keyword-only, default None): a torch.distributed process group over
     which the fp32 weight gradients are summed before they are rounded to the I/O dtype, for
-    sequence-sharded data parallel runs.
+    sequence-sharded data parallel runs;
+  * widths the tensor-core kernels do not take directly (the reference's production shape is
+    d_q = 968, d_kv = 216, test_smoke.py:54-57) are zero-padded here to d_kv = 256 and to the next
+    multiple of 256 for d_q, with differentiable torch ops, so the gradients come back in the
+    caller's widths.  Zero columns of q_raw / X and zero rows of the weights change neither the
+    scores nor the outputs.
 """
 from __future__ import annotations
 
@@ -229,6 +234,26 @@ class _TargetAttnInner(torch.autograd.Function):
         return du, dX, dW_V, None, None, None
 
 
+def _padded_widths(dtype: torch.dtype, d_q: Optional[int], d_kv: int, H: int) -> Optional[Tuple[Optional[int], int]]:
+    """(d_q, d_kv) to pad to so that the tcgen05 kernels apply, or None to leave the inputs alone."""
+    if os.environ.get("VAFA_IMPL", "auto").lower() == "simt":
+        return None
+    if dtype not in (torch.bfloat16, torch.float16) or d_kv > 256 or H < 1 or 128 % H != 0:
+        return None
+    d_q_pad = None if d_q is None else max(256, (d_q + 255) // 256 * 256)
+    if d_kv == 256 and d_q_pad == d_q:
+        return None
+    return d_q_pad, 256
+
+
+def _pad_last(t: torch.Tensor, width: int) -> torch.Tensor:
+    return t if t.shape[-1] == width else torch.nn.functional.pad(t, (0, width - t.shape[-1]))
+
+
+def _pad_first(t: torch.Tensor, rows: int) -> torch.Tensor:
+    return t if t.shape[0] == rows else torch.nn.functional.pad(t, (0, 0) * (t.dim() - 1) + (0, rows - t.shape[0]))
+
+
 def _next_pow2(x: int) -> int:
     if x < 1:
         raise ValueError(f"expected positive dimension, got {x}")
@@ -274,6 +299,9 @@ def target_attn_inner(
     cu_k = cu_seqlens_k.to(device=u.device, dtype=torch.int32).contiguous()
     if validate:
         _validate(cu_q, cu_k, T_q, T_k)
+    pad = _padded_widths(u.dtype, None, d_kv, H)
+    if pad is not None:
+        u, X, W_V = _pad_last(u, pad[1]), _pad_last(X, pad[1]), _pad_first(W_V, pad[1])
     O, _ = _TargetAttnInner.apply(u.contiguous(), X.contiguous(), W_V.contiguous(), cu_q, cu_k, float(scale))
     return O
 
@@ -332,6 +360,10 @@ def packed_target_attn(
     cu_k = cu_seqlens_k.to(device=q_raw.device, dtype=torch.int32).contiguous()
     if validate:
         _validate(cu_q, cu_k, T_q, T_k)
+    pad = _padded_widths(q_raw.dtype, d_q, d_kv, H)
+    if pad is not None:
+        q_raw, W_Q = _pad_last(q_raw, pad[0]), _pad_first(W_Q, pad[0])
+        X, W_K, W_V = _pad_last(X, pad[1]), _pad_first(W_K, pad[1]), _pad_first(W_V, pad[1])
     O, _ = _PackedTargetAttn.apply(q_raw.contiguous(), X.contiguous(), W_Q.contiguous(), W_K.contiguous(),
                                    W_V.contiguous(), cu_q, cu_k, float(scale), weight_grad_group)
     return O

@@ -1,8 +1,10 @@
-// Dense product with a 256-deep reduction for the absorb operator's prologue and epilogue:
-//   C[M, N] = A[M, 256] . B[256, N]        (16-bit operands, fp32 accumulation, 16-bit result)
-// One persistent CTA per SM keeps its 256 x 256 slice of B in shared memory (128 KB, MN-major)
-// and streams 128-row tiles of A through a second buffer; the accumulator (256 TMEM columns) is
-// double buffered so the epilogue of tile i overlaps the load and MMAs of tile i+1.
+// Dense product for the absorb operator's prologue and epilogue:
+//   C[M, N] = A[M, K] . B[K, N]        (16-bit operands, fp32 accumulation, 16-bit result; K = 256 k)
+// K = 256: one persistent CTA per SM keeps its 256 x 256 slice of B in shared memory (128 KB,
+// MN-major) and streams 128-row tiles of A through a second buffer.  K = 512, 768, ...: the B slice of
+// each 256-deep chunk is streamed with the A chunk instead and the chunks accumulate in TMEM.  The
+// accumulator (256 TMEM columns) is double buffered so the epilogue of tile i overlaps the load and
+// MMAs of tile i+1.
 // It stands in for the two torch matmuls of the reference's prologue
 // (triton_target_attn_absorb/triton_target_attn_absorb/interface.py:434-435, here as one product
 // with the pre-multiplied W_Q W_K^T) and for the per-head W_V projection the reference does at the
@@ -38,6 +40,7 @@ struct GemmParams {
   int ldc;
   int n_tiles;     // N / 256
   int m_tiles;     // ceil(M / 128)
+  int k_chunks;    // K / 256
   int diag_heads;  // 0: full rows
 };
 
@@ -79,34 +82,46 @@ gemm_nn_k256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 4) {
     if (lane == 0) {
-      mbar_expect_tx(smem_u32(&sm.b_full), 4 * kK * 128);
-      for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(sm.b[c]), &tmap_b, smem_u32(&sm.b_full), n_tile * kNTile + c * 64, 0, 0);
+      const bool resident = p.k_chunks == 1;
+      if (resident) {
+        mbar_expect_tx(smem_u32(&sm.b_full), 4 * kK * 128);
+        for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(sm.b[c]), &tmap_b, smem_u32(&sm.b_full), n_tile * kNTile + c * 64, 0, 0);
+      }
       uint32_t it = 0;
-      for (int m = m_first; m < p.m_tiles; m += groups, ++it) {
-        if (!mbar_wait(smem_u32(&sm.a_empty), (it & 1) ^ 1, abort_flag)) break;
-        mbar_expect_tx(smem_u32(&sm.a_full), 4 * 128 * 128);
-        for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(sm.a[c]), &tmap_a, smem_u32(&sm.a_full), c * 64, 0, m * 128);
+      bool alive = true;
+      for (int m = m_first; alive && m < p.m_tiles; m += groups) {
+        for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
+          if (!mbar_wait(smem_u32(&sm.a_empty), (it & 1) ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.a_full), 4 * 128 * 128 + (resident ? 0 : 4 * kK * 128));
+          for (int c = 0; c < 4; ++c)
+            tma_load_3d(smem_u32(sm.a[c]), &tmap_a, smem_u32(&sm.a_full), kc * kK + c * 64, 0, m * 128);
+          if (!resident)
+            for (int c = 0; c < 4; ++c)
+              tma_load_3d(smem_u32(sm.b[c]), &tmap_b, smem_u32(&sm.a_full), n_tile * kNTile + c * 64, 0, kc * kK);
+        }
       }
     }
   } else if (warp == 5) {
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
       constexpr uint32_t idesc = make_idesc(kFmt, 0, 1, 128, kNTile);
-      bool ok = mbar_wait(smem_u32(&sm.b_full), 0, abort_flag);
-      uint32_t it = 0;
-      for (int m = m_first; ok && m < p.m_tiles; m += groups, ++it) {
-        const uint32_t buf = it & 1;
-        if (!mbar_wait(smem_u32(&sm.acc_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag)) break;
-        if (!mbar_wait(smem_u32(&sm.a_full), it & 1, abort_flag)) break;
-        tc_fence_after();
+      bool ok = p.k_chunks > 1 || mbar_wait(smem_u32(&sm.b_full), 0, abort_flag);
+      uint32_t it = 0, tile = 0;
+      for (int m = m_first; ok && m < p.m_tiles; m += groups, ++tile) {
+        const uint32_t buf = tile & 1;
+        if (!mbar_wait(smem_u32(&sm.acc_empty[buf]), ((tile >> 1) & 1) ^ 1, abort_flag)) break;
+        for (int kc = 0; kc < p.k_chunks; ++kc, ++it) {
+          if (!mbar_wait(smem_u32(&sm.a_full), it & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < kK / 16; ++kk) {
-          const uint64_t da = make_desc_sw128(smem_u32(sm.a[kk >> 2]) + (kk & 3) * 32, 16, 1024);
-          const uint64_t db = make_desc_sw128(smem_u32(sm.b[0]) + kk * 2048, kK * 128, 1024);
-          mma_ss(tbase + buf * kNTile, da, db, idesc, kk > 0);
+          for (int kk = 0; kk < kK / 16; ++kk) {
+            const uint64_t da = make_desc_sw128(smem_u32(sm.a[kk >> 2]) + (kk & 3) * 32, 16, 1024);
+            const uint64_t db = make_desc_sw128(smem_u32(sm.b[0]) + kk * 2048, kK * 128, 1024);
+            mma_ss(tbase + buf * kNTile, da, db, idesc, (kc > 0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&sm.a_empty));
         }
-        mma_commit(smem_u32(&sm.a_empty));
-        mma_commit(smem_u32(&sm.acc_full[buf]));
+        if (ok) mma_commit(smem_u32(&sm.acc_full[buf]));
       }
     }
   } else {
@@ -181,15 +196,17 @@ int sm100_gemm_nn_k256(const GemmNNArgs& g, cudaStream_t s) {
   GemmParams p;
   p.C = g.C; p.M = g.M; p.ldc = g.ldc; p.n_tiles = g.N / kNTile; p.m_tiles = (int)((g.M + 127) / 128);
   p.diag_heads = g.diag_heads;
+  p.k_chunks = g.lda / kK;
   int groups = sms / p.n_tiles;
   if (groups < 1) groups = 1;
   if (groups > p.m_tiles) groups = p.m_tiles;
   const int grid = groups * p.n_tiles;
   CUtensorMap ta, tb;
   int rc;
-  if (g.lda != kK || g.ldb != g.N) return fail(VAFA_ERR_UNSUPPORTED, "gemm_nn_k256: operands must be densely packed");
-  if ((rc = encode_tmap_rows(&ta, g.A, g.dtype, g.M, 1, kK, 128))) return rc;
-  if ((rc = encode_tmap_rows(&tb, g.B, g.dtype, kK, 1, g.N, 256))) return rc;
+  // K = lda (A rows densely packed), a multiple of 256; B is [K, N] densely packed
+  if (g.lda < kK || g.lda % kK != 0 || g.ldb != g.N) return fail(VAFA_ERR_UNSUPPORTED, "gemm_nn_k256: K=%d ldb=%d not supported", g.lda, g.ldb);
+  if ((rc = encode_tmap_rows(&ta, g.A, g.dtype, g.M, 1, g.lda, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tb, g.B, g.dtype, g.lda, 1, g.N, 256))) return rc;
   const size_t smem = sizeof(GemmSmem) + 1024;
   LaunchScope scope(kKAbsorbGemm, s);
   if (g.dtype == VAFA_BF16) {

@@ -228,27 +228,27 @@ int sm100_gemm_tn(const GemmTNArgs& g, cudaStream_t s) {
 namespace vafa {
 namespace {
 template <typename T>
-__global__ void __launch_bounds__(256) transpose_square_kernel(const T* __restrict__ in, T* __restrict__ out, int n) {
+__global__ void __launch_bounds__(256) transpose_kernel(const T* __restrict__ in, T* __restrict__ out, int rows, int cols) {
   __shared__ T tile[32][33];
-  const int bx = blockIdx.x * 32, by = blockIdx.y * 32;
+  const int bx = blockIdx.x * 32, by = blockIdx.y * 32;    // bx over columns, by over rows of `in`
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
   for (int j = ty; j < 32; j += 8)
-    if (by + j < n && bx + tx < n) tile[j][tx] = in[(long long)(by + j) * n + bx + tx];
+    if (by + j < rows && bx + tx < cols) tile[j][tx] = in[(long long)(by + j) * cols + bx + tx];
   __syncthreads();
   for (int j = ty; j < 32; j += 8)
-    if (bx + j < n && by + tx < n) out[(long long)(bx + j) * n + by + tx] = tile[tx][j];
+    if (bx + j < cols && by + tx < rows) out[(long long)(bx + j) * rows + by + tx] = tile[tx][j];
 }
 }  // namespace
 
-// out[j][i] = in[i][j] for an n x n 16-bit matrix.
-int sm100_transpose_square(const void* in, void* out, int n, int dtype, cudaStream_t s) {
+// out[j][i] = in[i][j] for a rows x cols 16-bit matrix (out is cols x rows).
+int sm100_transpose(const void* in, void* out, int rows, int cols, int dtype, cudaStream_t s) {
   LaunchScope scope(kKCast, s);
-  dim3 grid((n + 31) / 32, (n + 31) / 32);
+  dim3 grid((cols + 31) / 32, (rows + 31) / 32);
   if (dtype == VAFA_BF16)
-    transpose_square_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, n);
+    transpose_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, rows, cols);
   else
-    transpose_square_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in, (__half*)out, n);
-  VAFA_LAUNCH_CHECK("transpose_square_kernel");
+    transpose_kernel<__half><<<grid, 256, 0, s>>>((const __half*)in, (__half*)out, rows, cols);
+  VAFA_LAUNCH_CHECK("transpose_kernel");
   return 0;
 }
 }  // namespace vafa

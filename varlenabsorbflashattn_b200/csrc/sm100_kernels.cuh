@@ -65,8 +65,8 @@ int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);
 int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s);
 int sm100_absorb_expand_wv(const void* w_v, void* bexp, int H, int D_H, int d_kv, int dtype, cudaStream_t s);
 
-// C[M, ldc] (16-bit) = A[M, 256] . B[256, N] with A rows K-major (row stride lda elements) and B
-// row-major [256, N] (N a multiple of 256, row stride ldb).  diag_heads > 0: row m keeps only the
+// C[M, ldc] (16-bit) = A[M, K] . B[K, N] with A rows densely packed (K = lda, a multiple of 256) and B
+// row-major [K, N] (N a multiple of 256, row stride ldb = N).  diag_heads > 0: row m keeps only the
 // 256/diag_heads columns of block (m % diag_heads) and writes them to C[m, 0 : 256/diag_heads]
 // (per-head projection of head-stacked rows); N must then be 256.
 struct GemmNNArgs {
@@ -87,6 +87,6 @@ struct GemmTNArgs {
 };
 size_t sm100_gemm_tn_workspace_bytes(long long T, int batch, int n_keep, int sm_count);
 int sm100_gemm_tn(const GemmTNArgs& g, cudaStream_t s);
-int sm100_transpose_square(const void* in, void* out, int n, int dtype, cudaStream_t s);
+int sm100_transpose(const void* in, void* out, int rows, int cols, int dtype, cudaStream_t s);
 
 }  // namespace vafa

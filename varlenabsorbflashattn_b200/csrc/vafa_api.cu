@@ -143,7 +143,7 @@ SimtAttnParams simt_from_absorb(const vafa_absorb_args* a, const void* u, void* 
 // Which parts of the absorb forward run on the tcgen05 kernels.
 struct AbsorbFast {
   bool core;      // attention over X: 16-bit, d_kv == 256, H divides 128
-  bool prologue;  // u = q_raw (W_Q W_K^T): core && d_q == 256
+  bool prologue;  // u = q_raw (W_Q W_K^T): core && d_q a multiple of 256
   bool epilogue;  // O = axn W_V per head: core && H * D_H == 256 && D_H >= 32
 };
 
@@ -154,7 +154,7 @@ AbsorbFast absorb_fast(const vafa_absorb_args* a, bool inner) {
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
   f.core = (a->dtype == VAFA_BF16 || a->dtype == VAFA_F16) && a->d_kv == 256 && H >= 1 && H <= 128 && (128 % H) == 0 &&
            a->total_q > 0 && a->total_k > 0 && a->scale > 0.f && al(a->q_raw) && al(a->x) && al(a->o) && al(a->saved);
-  f.prologue = f.core && !inner && a->d_q == 256 && al(a->w_q) && al(a->w_k);
+  f.prologue = f.core && !inner && a->d_q >= 256 && a->d_q % 256 == 0 && al(a->w_q) && al(a->w_k);
   f.epilogue = f.core && H * a->head_dim == 256 && a->head_dim >= 32 && al(a->w_v);
   return f;
 }
@@ -236,9 +236,10 @@ AbsorbBwdExtra absorb_bwd_extra(const vafa_absorb_args* a) {
   x.bexp = align_up(H * a->head_dim * H * a->d_kv * elem_size(a->dtype), 256);
   x.sched = sm100_absorb_core_bwd_workspace_bytes(a->total_q, a->total_k, a->n_seg, a->num_heads);
   const size_t t1 = sm100_gemm_tn_workspace_bytes(a->total_q, a->num_heads, 32, a->sm_count);
-  const size_t t2 = sm100_gemm_tn_workspace_bytes(a->total_q, 1, 256, a->sm_count);
+  const int q_chunks = a->d_q >= 256 ? a->d_q / 256 : 1;
+  const size_t t2 = sm100_gemm_tn_workspace_bytes(a->total_q, q_chunks, 256, a->sm_count);
   x.tn = t1 > t2 ? t1 : t2;
-  x.wqt = align_up((size_t)256 * 256 * elem_size(a->dtype), 256);
+  x.wqt = align_up((size_t)256 * (a->d_q > 256 ? a->d_q : 256) * elem_size(a->dtype), 256);
   return x;
 }
 
@@ -266,7 +267,7 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   int rc;
   // weight-gradient chain on the tensor-core GEMMs: needs the dU/dX fast path's preconditions, D_H = 32
   // (the 64-column box trick of the token reductions) and, for the full operator, d_q = 256
-  const bool fast_chain = absorb_bwd_core_fast(a, inner) && dh == 32 && (inner || dq == 256);
+  const bool fast_chain = absorb_bwd_core_fast(a, inner) && dh == 32 && (inner || (dq >= 256 && dq % 256 == 0));
   if (!inner && absorb_fast(a, false).prologue) {
     // the tcgen05 prologue goes straight to u; the weight-gradient chain below needs p = q_raw W_Q
     if (fast_chain) {
@@ -318,11 +319,14 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     // dW_K[kv,h,dd] = sum_t du[t,h,kv] p[t,h,dd]
     GemmTNArgs tk{du, p, dWK, tn_ws, Tq, a->dtype, H, H, 64, 32, H * dh, dh, dh, (long long)H * dh, a->sm_count};
     if ((rc = sm100_gemm_tn(tk, s))) return rc;
-    // dW_Q[a,(h,dd)] = sum_t q_raw[t,a] dp[t,(h,dd)]
-    GemmTNArgs tq{a->q_raw, dp, dWQ, tn_ws, Tq, a->dtype, 1, 1, 256, 256, H * dh, 0, 0, (long long)H * dh, a->sm_count};
+    // dW_Q[a,(h,dd)] = sum_t q_raw[t,a] dp[t,(h,dd)]: q_raw as d_q/256 column blocks ("heads") of 256,
+    // one batch entry per block, all against the same dp
+    const int q_chunks = dq / 256;
+    GemmTNArgs tq{a->q_raw, dp, dWQ, tn_ws, Tq, a->dtype, q_chunks, q_chunks, 256, 256, H * dh, 0,
+                  (long long)256 * H * dh, (long long)H * dh, a->sm_count};
     if ((rc = sm100_gemm_tn(tq, s))) return rc;
-    // dq_raw = dp W_Q^T
-    if ((rc = sm100_transpose_square(a->w_q, wqt, 256, a->dtype, s))) return rc;
+    // dq_raw = dp W_Q^T   (W_Q is [d_q, H*D_H]; its transpose [H*D_H, d_q])
+    if ((rc = sm100_transpose(a->w_q, wqt, dq, H * dh, a->dtype, s))) return rc;
     GemmNNArgs gq{dp, wqt, a->dq_raw, Tq, dq, H * dh, dq, dq, a->dtype, 0, a->sm_count};
     return sm100_gemm_nn_k256(gq, s);
   }
