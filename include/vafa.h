@@ -22,7 +22,7 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
-#define VAFA_ABI_VERSION 1
+#define VAFA_ABI_VERSION 2
 
 enum vafa_dtype { VAFA_F32 = 0, VAFA_BF16 = 1, VAFA_F16 = 2 };
 
@@ -149,6 +149,10 @@ typedef struct vafa_absorb_args {
   void* workspace;
   size_t workspace_bytes;
   int32_t* status;
+  int32_t x_width;      /* row width of x and dx in elements; 0 means d_kv.  A smaller width (a multiple
+                           of 8) is taken only by the tensor-core kernels: the missing columns read as
+                           zero (the weights must have d_kv rows, the extra ones zero) and dx is written
+                           x_width columns wide.  Lets a caller with d_kv < 256 pad only its weights. */
 } vafa_absorb_args;
 
 size_t vafa_absorb_saved_bytes(const vafa_absorb_args* a);

@@ -34,13 +34,14 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version(lib):
-    assert lib.vafa_abi_version() == 1
+    assert lib.vafa_abi_version() == 2
 
 
 def test_struct_sizes_match_header():
     # 11 pointers + 7 int32 + float + 3 int32 (+pad) + pointer + size_t + pointer
     assert C.sizeof(_lib.VarlenArgs) == 11 * 8 + 12 * 4 + 3 * 8
-    assert C.sizeof(_lib.AbsorbArgs) == 14 * 8 + 12 * 4 + 3 * 8
+    # ... + x_width (int32, padded to 8)
+    assert C.sizeof(_lib.AbsorbArgs) == 14 * 8 + 12 * 4 + 3 * 8 + 8
 
 
 def test_null_args_rejected(lib):

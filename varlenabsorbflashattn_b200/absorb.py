@@ -99,7 +99,8 @@ def prepare_target_attn_indices(cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.
     return _chunk_rows(cu_seqlens_q, _BT_Q), _chunk_rows(cu_seqlens_k, _BT_K)
 
 
-def _fill(a: _lib.AbsorbArgs, device, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, dtype, scale) -> None:
+def _fill(a: _lib.AbsorbArgs, device, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, dtype, scale, x_width=0) -> None:
+    a.x_width = 0 if x_width == d_kv else x_width
     a.cu_seqlens_q, a.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
     a.n_seg, a.total_q, a.total_k = cu_q.numel() - 1, T_q, T_k
     a.d_q, a.d_kv, a.num_heads, a.head_dim = d_q, d_kv, H, D_H
@@ -121,14 +122,15 @@ class _PackedTargetAttn(torch.autograd.Function):
     def forward(ctx, q_raw, X, W_Q, W_K, W_V, cu_q, cu_k, scale, group):
         lib = _lib.load()
         T_q, d_q = q_raw.shape
-        T_k, d_kv = X.shape
+        T_k, x_w = X.shape
+        d_kv = W_K.shape[0]  # X may be narrower than the (padded) weights: see _padded_widths
         _, H, D_H = W_Q.shape
         dev = q_raw.device
         O = torch.empty((T_q, H, D_H), dtype=q_raw.dtype, device=dev)
         lse = torch.empty((T_q, H), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             a = _lib.AbsorbArgs()
-            _fill(a, dev, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, q_raw.dtype, scale)
+            _fill(a, dev, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, q_raw.dtype, scale, x_w)
             a.q_raw, a.x, a.w_q, a.w_k, a.w_v = (t.data_ptr() for t in (q_raw, X, W_Q, W_K, W_V))
             a.o, a.lse = O.data_ptr(), lse.data_ptr()
             saved = torch.empty(max(1, lib.vafa_absorb_saved_bytes(a)), dtype=torch.uint8, device=dev)
@@ -146,7 +148,8 @@ class _PackedTargetAttn(torch.autograd.Function):
         q_raw, X, W_Q, W_K, W_V, O, lse, cu_q, cu_k, saved = ctx.saved_tensors
         lib = _lib.load()
         T_q, d_q = q_raw.shape
-        T_k, d_kv = X.shape
+        T_k, x_w = X.shape
+        d_kv = W_K.shape[0]
         _, H, D_H = W_Q.shape
         dev = q_raw.device
         if dO.dtype != q_raw.dtype:
@@ -158,7 +161,7 @@ class _PackedTargetAttn(torch.autograd.Function):
         dw = torch.empty(n_wq + 2 * n_wk, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             a = _lib.AbsorbArgs()
-            _fill(a, dev, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, q_raw.dtype, ctx.scale)
+            _fill(a, dev, cu_q, cu_k, T_q, T_k, d_q, d_kv, H, D_H, q_raw.dtype, ctx.scale, x_w)
             a.q_raw, a.x, a.w_q, a.w_k, a.w_v = (t.data_ptr() for t in (q_raw, X, W_Q, W_K, W_V))
             a.o, a.lse, a.saved, a.d_o = O.data_ptr(), lse.data_ptr(), saved.data_ptr(), dO.data_ptr()
             a.dq_raw, a.dx, a.dw = dq_raw.data_ptr(), dX.data_ptr(), dw.data_ptr()
@@ -187,14 +190,14 @@ class _TargetAttnInner(torch.autograd.Function):
     def forward(ctx, u, X, W_V, cu_q, cu_k, scale):
         lib = _lib.load()
         T_q, H, d_kv = u.shape
-        T_k = X.shape[0]
+        T_k, x_w = X.shape
         D_H = W_V.shape[2]
         dev = u.device
         O = torch.empty((T_q, H, D_H), dtype=u.dtype, device=dev)
         lse = torch.empty((T_q, H), dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             a = _lib.AbsorbArgs()
-            _fill(a, dev, cu_q, cu_k, T_q, T_k, 0, d_kv, H, D_H, u.dtype, scale)
+            _fill(a, dev, cu_q, cu_k, T_q, T_k, 0, d_kv, H, D_H, u.dtype, scale, x_w)
             a.q_raw, a.x, a.w_v = u.data_ptr(), X.data_ptr(), W_V.data_ptr()
             a.o, a.lse = O.data_ptr(), lse.data_ptr()
             saved = torch.empty(max(1, lib.vafa_absorb_saved_bytes(a)), dtype=torch.uint8, device=dev)
@@ -212,7 +215,7 @@ class _TargetAttnInner(torch.autograd.Function):
         u, X, W_V, O, lse, cu_q, cu_k, saved = ctx.saved_tensors
         lib = _lib.load()
         T_q, H, d_kv = u.shape
-        T_k = X.shape[0]
+        T_k, x_w = X.shape
         D_H = W_V.shape[2]
         dev = u.device
         if dO.dtype != u.dtype:
@@ -223,7 +226,7 @@ class _TargetAttnInner(torch.autograd.Function):
         dw = torch.empty(d_kv * H * D_H, dtype=torch.float32, device=dev)
         with torch.cuda.device(dev):
             a = _lib.AbsorbArgs()
-            _fill(a, dev, cu_q, cu_k, T_q, T_k, 0, d_kv, H, D_H, u.dtype, ctx.scale)
+            _fill(a, dev, cu_q, cu_k, T_q, T_k, 0, d_kv, H, D_H, u.dtype, ctx.scale, x_w)
             a.q_raw, a.x, a.w_v = u.data_ptr(), X.data_ptr(), W_V.data_ptr()
             a.o, a.lse, a.saved, a.d_o = O.data_ptr(), lse.data_ptr(), saved.data_ptr(), dO.data_ptr()
             a.dq_raw, a.dx, a.dw = du.data_ptr(), dX.data_ptr(), dw.data_ptr()
@@ -244,6 +247,12 @@ def _padded_widths(dtype: torch.dtype, d_q: Optional[int], d_kv: int, H: int) ->
     if d_kv == 256 and d_q_pad == d_q:
         return None
     return d_q_pad, 256
+
+
+def _narrow_x_ok(x_width: int, H: int, T_q: int, T_k: int) -> bool:
+    """X (the big tensor) can stay at its own width: the forward and backward tensor-core kernels read the
+    missing columns as zero through TMA and write dX at that width (vafa_absorb_args.x_width)."""
+    return x_width % 8 == 0 and 64 % H == 0 and T_q > 0 and T_k > 0
 
 
 def _pad_last(t: torch.Tensor, width: int) -> torch.Tensor:
@@ -301,7 +310,9 @@ def target_attn_inner(
         _validate(cu_q, cu_k, T_q, T_k)
     pad = _padded_widths(u.dtype, None, d_kv, H)
     if pad is not None:
-        u, X, W_V = _pad_last(u, pad[1]), _pad_last(X, pad[1]), _pad_first(W_V, pad[1])
+        u, W_V = _pad_last(u, pad[1]), _pad_first(W_V, pad[1])
+        if not _narrow_x_ok(d_kv, H, T_q, T_k):
+            X = _pad_last(X, pad[1])
     O, _ = _TargetAttnInner.apply(u.contiguous(), X.contiguous(), W_V.contiguous(), cu_q, cu_k, float(scale))
     return O
 
@@ -363,7 +374,9 @@ def packed_target_attn(
     pad = _padded_widths(q_raw.dtype, d_q, d_kv, H)
     if pad is not None:
         q_raw, W_Q = _pad_last(q_raw, pad[0]), _pad_first(W_Q, pad[0])
-        X, W_K, W_V = _pad_last(X, pad[1]), _pad_first(W_K, pad[1]), _pad_first(W_V, pad[1])
+        W_K, W_V = _pad_first(W_K, pad[1]), _pad_first(W_V, pad[1])
+        if not _narrow_x_ok(d_kv, H, T_q, T_k):
+            X = _pad_last(X, pad[1])
     O, _ = _PackedTargetAttn.apply(q_raw.contiguous(), X.contiguous(), W_Q.contiguous(), W_K.contiguous(),
                                    W_V.contiguous(), cu_q, cu_k, float(scale), weight_grad_group)
     return O

@@ -34,7 +34,7 @@ int sm100_varlen_bwd128_launch(const Bwd128Launch& L, cudaStream_t s);
 // in the I/O dtype; lse[t,h] log2-domain.  Requires d_kv == 256, 16-bit dtype, H dividing 128.
 struct AbsorbCoreArgs {
   const void* u;       // [T_q, H, 256]
-  const void* x;       // [T_k, 256]
+  const void* x;       // [T_k, x_width], x_width <= 256 (missing columns read as zero)
   void* axn;           // [T_q, H, 256]
   float* lse;          // [T_q, H]
   const int32_t* cu_q;
@@ -44,6 +44,7 @@ struct AbsorbCoreArgs {
   int sm_count;
   void* workspace;
   int32_t* status;
+  int x_width;
 };
 size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H);
 int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s);
@@ -59,6 +60,7 @@ struct AbsorbCoreBwdArgs {
   int sm_count;
   void* workspace;
   int32_t* status;
+  int x_width;         // row width of x and dx (<= 256)
 };
 size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H);
 int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);

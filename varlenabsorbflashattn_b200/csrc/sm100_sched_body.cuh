@@ -74,6 +74,31 @@ __device__ __forceinline__ int cost_bucket(long long c) {
 }
 
 
+// Walk all segments, one warp per segment (the body runs with all 32 lanes).  The cu_seqlens reads are
+// the latency of every pass, so a warp fetches `group` consecutive segments at once (one per lane,
+// coalesced) and hands them round by shuffle; group = n_seg / warps, at most 32, so that few segments
+// still spread over all warps.
+template <typename F>
+__device__ __forceinline__ void for_each_segment(const SchedParams& p, int lane, int wid, F body) {
+  constexpr int kWarps = kSchedThreads / 32;
+  const int group = max(1, min(32, p.n_seg / kWarps));
+  for (int s0 = wid * group; s0 < p.n_seg; s0 += kWarps * group) {
+    const int cnt = min(group, p.n_seg - s0);
+    Seg mine = {0, 0, 0, 0, 0, 0};
+    if (lane < cnt) mine = load_seg(p, s0 + lane);
+    for (int j = 0; j < cnt; ++j) {
+      Seg g;
+      g.q0 = __shfl_sync(0xffffffffu, mine.q0, j);
+      g.Lq = __shfl_sync(0xffffffffu, mine.Lq, j);
+      g.k0 = __shfl_sync(0xffffffffu, mine.k0, j);
+      g.Lk = __shfl_sync(0xffffffffu, mine.Lk, j);
+      g.off = g.Lk - g.Lq;
+      g.n_tiles = __shfl_sync(0xffffffffu, mine.n_tiles, j);
+      body(s0 + j, g);
+    }
+  }
+}
+
 __device__ __forceinline__ void sched_build(const SchedParams& p) {
   __shared__ int s_hist[kBuckets];
   __shared__ int s_units, s_items, s_rows, s_bs, s_combine;
@@ -91,13 +116,12 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   {
     int units = 0;
     long long blocks = 0;
-    for (int s = wid; s < p.n_seg; s += kWarps) {
-      const Seg g = load_seg(p, s);
+    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
       for (int t = lane; t < g.n_tiles; t += 32) {
         const Unit u = make_unit(p, g, t);
         if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
       }
-    }
+    });
     if (units) { atomicAdd(&s_units, units); atomicAdd((unsigned long long*)&s_blocks, (unsigned long long)blocks); }
   }
   __syncthreads();
@@ -126,15 +150,14 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
     __syncthreads();
     const int bs = s_bs;
     int items = 0, rows = 0;
-    for (int s = wid; s < p.n_seg; s += kWarps) {
-      const Seg g = load_seg(p, s);
+    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
       for (int t = lane; t < g.n_tiles; t += 32) {
         const Unit u = make_unit(p, g, t);
         const int ns = n_splits(n_blocks(u.i_len), bs);
         items += ns;
         if (ns > 1) rows += ns * u.o_rows;
       }
-    }
+    });
     if (items) atomicAdd(&s_items, items);
     if (rows) atomicAdd(&s_rows, rows);
     __syncthreads();
@@ -147,8 +170,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   const int bs = s_bs;
 
   // pass 3: items per cost bucket of their segment
-  for (int s = wid; s < p.n_seg; s += kWarps) {
-    const Seg g = load_seg(p, s);
+  for_each_segment(p, lane, wid, [&](int, const Seg& g) {
     long long cost = 0;
     int items = 0;
     for (int t = lane; t < g.n_tiles; t += 32) {
@@ -163,7 +185,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
       items += __shfl_xor_sync(0xffffffffu, items, o);
     }
     if (lane == 0 && items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
-  }
+  });
   __syncthreads();
   // descending exclusive scan: a bucket starts after all buckets of larger cost
   if (wid == 0) {
@@ -189,8 +211,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
 
   // pass 4: emit, one contiguous range per segment; one warp per segment, lanes over (head, tile)
   if (!overflow) {
-    for (int s = wid; s < p.n_seg; s += kWarps) {
-      const Seg g = load_seg(p, s);
+    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
       int items = 0, pos = 0, n_split_tiles = 0, c0 = 0;
       long long cost = 0;
       for (int t = lane; t < g.n_tiles; t += 32) {
@@ -229,7 +250,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
       n_split_tiles = __shfl_sync(0xffffffffu, n_split_tiles, 0);
       c0 = __shfl_sync(0xffffffffu, c0, 0);
       __syncwarp();
-      if (items == 0) continue;
+      if (items == 0) return;
       if (n_split_tiles == 0) {
         // one item per tile: position is direct
         // lanes over tiles (the unit is computed once), then one store per head
@@ -268,7 +289,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
           }
         }
       }
-    }
+    });
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -34,7 +34,8 @@ int encode_tmap_rows(CUtensorMap* m, const void* base, int dtype, long long rows
   if (!enc) return fail(VAFA_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if (dtype != VAFA_BF16 && dtype != VAFA_F16) return fail(VAFA_ERR_UNSUPPORTED, "tensor maps are built for 16-bit types only");
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return fail(VAFA_ERR_INVALID, "tensor base must be 16-byte aligned");
-  if (dim % 64 != 0 || box_rows < 1 || box_rows > 256 || box_heads < 1 || box_heads > heads || box_heads * box_rows > 256)
+  // the row width need not fill the last 64-column box: columns past it read as zero
+  if (dim < 8 || dim % 8 != 0 || box_rows < 1 || box_rows > 256 || box_heads < 1 || box_heads > heads || box_heads * box_rows > 256)
     return fail(VAFA_ERR_INVALID, "bad tensor map shape");
   cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)heads, (cuuint64_t)(rows > 0 ? rows : 1)};
   cuuint64_t strides[2] = {(cuuint64_t)dim * 2, (cuuint64_t)heads * dim * 2};

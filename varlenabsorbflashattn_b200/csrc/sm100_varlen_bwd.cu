@@ -82,6 +82,7 @@ struct BwdParams {
   float scale;
   float scale_log2;
   int32_t* status;
+  int out_width;         // absorb dX: columns written per row (= row stride of the output), <= D
 };
 
 // kAbsorb = false: items x heads; outer/inner operands are per-head [rows, D] slices.
@@ -384,8 +385,10 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       const long long out_row = kAbsorb ? (kDKV ? (long long)w.o_start + r : (long long)w.o_start * p.H + r)
                                         : ((long long)w.o_start + r) * p.H + h;
 #pragma unroll
+      // absorb dX rows are out_width wide (the caller's X may be narrower than the 256-column tile)
+      const int out_w = (kAbsorb && kDKV) ? p.out_width : D;
       for (int which = 0; which < ((kDKV && !kAbsorb) ? 2 : 1); ++which) {
-        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * D;
+        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * out_w;
         // dV unscaled; dQ, dK and dU scaled here; absorb dX carries the scale inside dS
         const float mul = (kDKV && (which == 0)) ? 1.f : p.scale;
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
@@ -409,7 +412,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
               u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * mul, __uint_as_float(t[8 * v4 + 3]) * mul);
               u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * mul, __uint_as_float(t[8 * v4 + 5]) * mul);
               u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * mul, __uint_as_float(t[8 * v4 + 7]) * mul);
-              dst[v4] = u;
+              if (cc * 32 + v4 * 8 < out_w) dst[v4] = u;
             }
           }
         }
@@ -646,13 +649,14 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   CUtensorMap u128, g128, x64, x128, u64, g64;
   if ((rc = encode_tmap_rows(&u128, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
   if ((rc = encode_tmap_rows(&g128, a.dax, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
-  if ((rc = encode_tmap_rows(&x64, a.x, a.dtype, a.total_k, 1, D, kInner))) return rc;
-  if ((rc = encode_tmap_rows(&x128, a.x, a.dtype, a.total_k, 1, D, kTile))) return rc;
+  if ((rc = encode_tmap_rows(&x64, a.x, a.dtype, a.total_k, 1, a.x_width, kInner))) return rc;
+  if ((rc = encode_tmap_rows(&x128, a.x, a.dtype, a.total_k, 1, a.x_width, kTile))) return rc;
   if ((rc = encode_tmap_rows(&u64, a.u, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
   if ((rc = encode_tmap_rows(&g64, a.dax, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
 
   BwdParams p;
   p.ld = (const float2*)a.ld; p.ld_stride = 0; p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
+  p.out_width = a.x_width;
   p.out1 = nullptr;
   {
     p.out0 = a.du; p.header = sq.header; p.items = sq.items;

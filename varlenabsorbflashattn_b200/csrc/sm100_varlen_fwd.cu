@@ -665,7 +665,7 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   if (rc) return rc;
   CUtensorMap tu, tx;
   if ((rc = encode_tmap_rows(&tu, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
-  if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, a.x_width, 128))) return rc;
   FwdParams p;
   p.o = a.axn; p.lse = a.lse; p.partial_o = nullptr; p.partial_lse = nullptr;
   p.header = sp.header; p.items = sp.items; p.H = a.H;

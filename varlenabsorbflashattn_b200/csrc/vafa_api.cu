@@ -105,6 +105,9 @@ AbsorbSizes absorb_sizes(const vafa_absorb_args* a) {
   return z;
 }
 
+// Row width of x / dx: d_kv unless the caller says its rows are narrower.
+int x_width_of(const vafa_absorb_args* a) { return a->x_width > 0 ? a->x_width : a->d_kv; }
+
 int check_absorb(const vafa_absorb_args* a, bool bwd, bool inner) {
   if (!a) return fail(VAFA_ERR_INVALID, "null args");
   if (!valid_dtype(a->dtype)) return fail(VAFA_ERR_INVALID, "bad dtype %d", a->dtype);
@@ -207,7 +210,7 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   }
   if (fast.core) {
     AbsorbCoreArgs c{u, a->x, axn, a->lse, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H, a->dtype,
-                     a->scale, a->sm_count, ws, a->status};
+                     a->scale, a->sm_count, ws, a->status, x_width_of(a)};
     if ((rc = sm100_absorb_core_fwd(c, s))) return rc;
   } else {
     SimtAttnParams p = simt_from_absorb(a, u, axn);
@@ -291,7 +294,7 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     if ((rc = sm100_gemm_nn_k256(gd, s))) return rc;
     if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->dtype, s))) return rc;
     AbsorbCoreBwdArgs cb{u, a->x, dax, ld, du, a->dx, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H,
-                         a->dtype, a->scale, a->sm_count, sched, a->status};
+                         a->dtype, a->scale, a->sm_count, sched, a->status, x_width_of(a)};
     if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
   } else {
     // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
@@ -430,9 +433,19 @@ size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a) {
   return n;
 }
 
+// x rows narrower than d_kv exist only for the tensor-core kernels (TMA fills the missing columns)
+static int check_x_width(const vafa_absorb_args* a, bool fast) {
+  const int xw = x_width_of(a);
+  if (xw == a->d_kv) return 0;
+  if (xw > a->d_kv || xw % 8 != 0) return fail(VAFA_ERR_INVALID, "x_width %d must be a multiple of 8 and at most d_kv %d", xw, a->d_kv);
+  if (!fast) return fail(VAFA_ERR_UNSUPPORTED, "x_width %d < d_kv %d needs the tcgen05 kernels for this shape", xw, a->d_kv);
+  return 0;
+}
+
 int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, false, false);
   if (rc) return rc;
+  if ((rc = check_x_width(a, absorb_fast(a, false).core))) return rc;
   const int impl = pick_impl(a->impl, absorb_fast(a, false).core, "absorb_fwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, false)))) return rc;
@@ -441,6 +454,7 @@ int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
 int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, false);
   if (rc) return rc;
+  if ((rc = check_x_width(a, absorb_bwd_core_fast(a, false)))) return rc;
   const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
@@ -449,6 +463,7 @@ int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
 int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, false, true);
   if (rc) return rc;
+  if ((rc = check_x_width(a, absorb_fast(a, true).core))) return rc;
   const int impl = pick_impl(a->impl, absorb_fast(a, true).core, "absorb_inner_fwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, true)))) return rc;
@@ -457,6 +472,7 @@ int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
 int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, true);
   if (rc) return rc;
+  if ((rc = check_x_width(a, absorb_bwd_core_fast(a, true)))) return rc;
   const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_inner_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
