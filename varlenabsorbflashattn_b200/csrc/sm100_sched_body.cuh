@@ -74,28 +74,23 @@ __device__ __forceinline__ int cost_bucket(long long c) {
 }
 
 
-// Walk all segments, one warp per segment (the body runs with all 32 lanes).  The cu_seqlens reads are
-// the latency of every pass, so a warp fetches `group` consecutive segments at once (one per lane,
-// coalesced) and hands them round by shuffle; group = n_seg / warps, at most 32, so that few segments
-// still spread over all warps.
+// Walk all segments with G lanes per segment (G a power of two, 1..32, the same for the whole list):
+// lane gl of a group owns tiles gl, gl + G, ... of its segment.  G = 1024 / n_seg rounded up to a power
+// of two: few long segments get a whole warp each, a batch of a thousand users one thread each (with a
+// warp per one-tile segment the list of 1137 users cost 32 times the instructions).  Every group runs
+// the same number of rounds (the body contains warp shuffles); groups past the end get an empty segment.
+// Neighbouring groups read neighbouring cu_seqlens entries, so one round costs one memory latency.
+// body(g, gl, G)
 template <typename F>
-__device__ __forceinline__ void for_each_segment(const SchedParams& p, int lane, int wid, F body) {
-  constexpr int kWarps = kSchedThreads / 32;
-  const int group = max(1, min(32, p.n_seg / kWarps));
-  for (int s0 = wid * group; s0 < p.n_seg; s0 += kWarps * group) {
-    const int cnt = min(group, p.n_seg - s0);
-    Seg mine = {0, 0, 0, 0, 0, 0};
-    if (lane < cnt) mine = load_seg(p, s0 + lane);
-    for (int j = 0; j < cnt; ++j) {
-      Seg g;
-      g.q0 = __shfl_sync(0xffffffffu, mine.q0, j);
-      g.Lq = __shfl_sync(0xffffffffu, mine.Lq, j);
-      g.k0 = __shfl_sync(0xffffffffu, mine.k0, j);
-      g.Lk = __shfl_sync(0xffffffffu, mine.Lk, j);
-      g.off = g.Lk - g.Lq;
-      g.n_tiles = __shfl_sync(0xffffffffu, mine.n_tiles, j);
-      body(s0 + j, g);
-    }
+__device__ __forceinline__ void for_each_segment(const SchedParams& p, int G, F body) {
+  const int per_round = kSchedThreads / G;
+  const int gid = threadIdx.x / G, gl = threadIdx.x % G;
+  const int rounds = (p.n_seg + per_round - 1) / per_round;
+  for (int it = 0; it < rounds; ++it) {
+    const int s = it * per_round + gid;
+    Seg g = {0, 0, 0, 0, 0, 0};
+    if (s < p.n_seg) g = load_seg(p, s);
+    body(g, gl, G);
   }
 }
 
@@ -108,16 +103,17 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   for (int b = threadIdx.x; b < kBuckets; b += kSchedThreads) s_hist[b] = 0;
   __syncthreads();
 
-  // Every pass: one warp per segment, lanes over the segment's tiles.
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  constexpr int kWarps = kSchedThreads / 32;
+  // lanes per segment (see for_each_segment)
+  int G = 1;
+  while (G < 32 && G * p.n_seg < kSchedThreads) G <<= 1;
 
   // pass 1: totals
   {
     int units = 0;
     long long blocks = 0;
-    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
-      for (int t = lane; t < g.n_tiles; t += 32) {
+    for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
+      for (int t = t0; t < g.n_tiles; t += ts) {
         const Unit u = make_unit(p, g, t);
         if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
       }
@@ -150,8 +146,8 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
     __syncthreads();
     const int bs = s_bs;
     int items = 0, rows = 0;
-    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
-      for (int t = lane; t < g.n_tiles; t += 32) {
+    for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
+      for (int t = t0; t < g.n_tiles; t += ts) {
         const Unit u = make_unit(p, g, t);
         const int ns = n_splits(n_blocks(u.i_len), bs);
         items += ns;
@@ -170,21 +166,20 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   const int bs = s_bs;
 
   // pass 3: items per cost bucket of their segment
-  for_each_segment(p, lane, wid, [&](int, const Seg& g) {
+  for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
     long long cost = 0;
     int items = 0;
-    for (int t = lane; t < g.n_tiles; t += 32) {
+    for (int t = t0; t < g.n_tiles; t += ts) {
       const Unit u = make_unit(p, g, t);
       const int nb = n_blocks(u.i_len);
       cost += nb;
       items += n_splits(nb, bs);
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = ts >> 1; o > 0; o >>= 1) {
       cost += __shfl_xor_sync(0xffffffffu, cost, o);
       items += __shfl_xor_sync(0xffffffffu, items, o);
     }
-    if (lane == 0 && items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+    if (t0 == 0 && items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
   });
   __syncthreads();
   // descending exclusive scan: a bucket starts after all buckets of larger cost
@@ -211,23 +206,22 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
 
   // pass 4: emit, one contiguous range per segment; one warp per segment, lanes over (head, tile)
   if (!overflow) {
-    for_each_segment(p, lane, wid, [&](int, const Seg& g) {
+    for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
       int items = 0, pos = 0, n_split_tiles = 0, c0 = 0;
       long long cost = 0;
-      for (int t = lane; t < g.n_tiles; t += 32) {
+      for (int t = t0; t < g.n_tiles; t += ts) {
         const int nb = n_blocks(make_unit(p, g, t).i_len);
         const int ns = n_splits(nb, bs);
         cost += nb;
         items += ns;
         n_split_tiles += (ns > 1);
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
+      for (int o = ts >> 1; o > 0; o >>= 1) {
         cost += __shfl_xor_sync(0xffffffffu, cost, o);
         items += __shfl_xor_sync(0xffffffffu, items, o);
         n_split_tiles += __shfl_xor_sync(0xffffffffu, n_split_tiles, o);
       }
-      if (lane == 0) {
+      if (t0 == 0) {
         if (items) pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
         if (n_split_tiles) {
           // split-K bookkeeping once per tile: the partial rows are shared by the heads ([row][head])
@@ -245,16 +239,17 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
           }
         }
       }
-      items = __shfl_sync(0xffffffffu, items, 0);
-      pos = __shfl_sync(0xffffffffu, pos, 0);
-      n_split_tiles = __shfl_sync(0xffffffffu, n_split_tiles, 0);
-      c0 = __shfl_sync(0xffffffffu, c0, 0);
-      __syncwarp();
+      if (ts > 1) {
+        // from the group's first lane; the combine units it wrote are read by all lanes below
+        pos = __shfl_sync(0xffffffffu, pos, 0, ts);
+        c0 = __shfl_sync(0xffffffffu, c0, 0, ts);
+        __syncwarp();
+      }
       if (items == 0) return;
       if (n_split_tiles == 0) {
         // one item per tile: position is direct
         // lanes over tiles (the unit is computed once), then one store per head
-        for (int t = lane; t < g.n_tiles; t += 32) {
+        for (int t = t0; t < g.n_tiles; t += ts) {
           const Unit u = make_unit(p, g, t);
           WorkItem w;
           w.o_start = u.o_start; w.o_rows = u.o_rows; w.i_start = u.i_start; w.i_len = u.i_len;
@@ -265,7 +260,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
           }
         }
       } else {
-        for (int h = lane; h < p.H; h += 32) {
+        for (int h = t0; h < p.H; h += ts) {
           int at = pos + h * items, k = 0;
           for (int t = 0; t < g.n_tiles; ++t) {
             const Unit u = make_unit(p, g, t);
