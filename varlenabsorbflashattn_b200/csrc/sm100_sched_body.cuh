@@ -74,6 +74,41 @@ __device__ __forceinline__ int cost_bucket(long long c) {
 }
 
 
+// Warp-aggregated histogram add: every lane of the warp calls; the `active` lanes add `v` to hist[bucket]
+// and get back the value before their own add.  Lanes that hit the same bucket are served by one atomic
+// (a thousand users of equal cost otherwise queue on one shared-memory word); their ranges are
+// consecutive in lane order.
+__device__ __forceinline__ int warp_hist_add(int* hist, bool active, int bucket, int v) {
+  const int lane = threadIdx.x & 31;
+  int pos = 0;
+  unsigned todo = __ballot_sync(0xffffffffu, active);
+  while (todo) {
+    const int leader = __ffs(todo) - 1;
+    const int b = __shfl_sync(0xffffffffu, bucket, leader);
+    const bool mine = active && bucket == b;
+    const unsigned same = __ballot_sync(0xffffffffu, mine);
+    int incl = mine ? v : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    int base = 0;
+    if (lane == leader) base = atomicAdd(&hist[b], total);
+    base = __shfl_sync(0xffffffffu, base, leader);
+    if (mine) pos = base + incl - v;
+    todo &= ~same;
+  }
+  return pos;
+}
+
+__device__ __forceinline__ long long warp_sum_ll(long long x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
 // Walk all segments with G lanes per segment (G a power of two, 1..32, the same for the whole list):
 // lane gl of a group owns tiles gl, gl + G, ... of its segment.  G = 1024 / n_seg rounded up to a power
 // of two: few long segments get a whole warp each, a batch of a thousand users one thread each (with a
@@ -118,7 +153,9 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
         if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
       }
     });
-    if (units) { atomicAdd(&s_units, units); atomicAdd((unsigned long long*)&s_blocks, (unsigned long long)blocks); }
+    units = (int)warp_sum_ll(units);
+    blocks = warp_sum_ll(blocks);
+    if (lane == 0 && units) { atomicAdd(&s_units, units); atomicAdd((unsigned long long*)&s_blocks, (unsigned long long)blocks); }
   }
   __syncthreads();
 
@@ -154,8 +191,10 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
         if (ns > 1) rows += ns * u.o_rows;
       }
     });
-    if (items) atomicAdd(&s_items, items);
-    if (rows) atomicAdd(&s_rows, rows);
+    items = (int)warp_sum_ll(items);
+    rows = (int)warp_sum_ll(rows);
+    if (lane == 0 && items) atomicAdd(&s_items, items);
+    if (lane == 0 && rows) atomicAdd(&s_rows, rows);
     __syncthreads();
     const bool fits = ((long long)s_items * p.H <= p.cap_items) && (s_rows <= p.cap_rows);
     __syncthreads();
@@ -179,7 +218,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
       cost += __shfl_xor_sync(0xffffffffu, cost, o);
       items += __shfl_xor_sync(0xffffffffu, items, o);
     }
-    if (t0 == 0 && items) atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
+    warp_hist_add(s_hist, t0 == 0 && items > 0, cost_bucket(cost), items * p.H);
   });
   __syncthreads();
   // descending exclusive scan: a bucket starts after all buckets of larger cost
@@ -221,8 +260,8 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
         items += __shfl_xor_sync(0xffffffffu, items, o);
         n_split_tiles += __shfl_xor_sync(0xffffffffu, n_split_tiles, o);
       }
+      pos = warp_hist_add(s_hist, t0 == 0 && items > 0, cost_bucket(cost), items * p.H);
       if (t0 == 0) {
-        if (items) pos = atomicAdd(&s_hist[cost_bucket(cost)], items * p.H);
         if (n_split_tiles) {
           // split-K bookkeeping once per tile: the partial rows are shared by the heads ([row][head])
           c0 = atomicAdd(&s_combine, n_split_tiles);
