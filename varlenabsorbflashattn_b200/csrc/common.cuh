@@ -69,6 +69,50 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return r;
 }
 
+// Coalesced store of a 32-column, 16-bit chunk (64 bytes) of each lane's row.
+// In the epilogues a thread owns one row of the tile (TMEM lane = row), so a plain store of its chunk
+// sends 32 lanes to 32 different rows: 32 memory requests of 16 bytes per instruction, which made the
+// store pipe, not the tensor pipe, the limit of short items.  Here the four lanes of a group first
+// transpose their 4 x 4 block of 16-byte pieces by shuffle, so that each store instruction writes 64
+// contiguous bytes of one row per group: 8 requests of 64 bytes.
+//   w          the lane's chunk as 16 packed words (16-byte pieces w[0..3], w[4..7], ...)
+//   my_chunk   address of the chunk in the lane's own row (the rows of a warp are `row_stride`
+//              elements apart, in lane order), 16-byte aligned
+//   my_row     index of the lane's row in the tile; rows >= n_rows are not written
+//   n_pieces   leading 16-byte pieces of the chunk that exist in the output (0..4)
+template <typename T>
+__device__ __forceinline__ void store_chunk_coalesced(uint32_t (&w)[16], T* my_chunk, long long row_stride, int my_row,
+                                                      int n_rows, int n_pieces) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int m = 1; m <= 2; m <<= 1) {
+    const bool hi = (lane & m) != 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j & m) continue;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        // low lane gives its piece j|m and takes the high lane's piece j
+        const uint32_t send = hi ? w[4 * j + e] : w[4 * (j | m) + e];
+        const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, m);
+        if (hi) w[4 * j + e] = recv; else w[4 * (j | m) + e] = recv;
+      }
+    }
+  }
+  // piece k now holds piece (lane & 3) of the row of lane (lane & ~3) + k
+  const int i = lane & 3;
+  if (i < n_pieces) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int row = my_row - i + k;
+      if (row < n_rows) {
+        uint4* dst = reinterpret_cast<uint4*>(my_chunk + (long long)(k - i) * row_stride) + i;
+        *dst = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);

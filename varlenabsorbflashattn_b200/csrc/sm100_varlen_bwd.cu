@@ -34,6 +34,15 @@ namespace {
 
 using namespace ptx;
 
+// Optional wait-time tracing (build with -DVAFA_TRACE), as in sm100_varlen_fwd.cu.
+#ifdef VAFA_TRACE
+#define TRACE_T0() const long long _t0 = clock64()
+#define TRACE_ADD(slot) tr[slot] += clock64() - _t0
+#else
+#define TRACE_T0()
+#define TRACE_ADD(slot)
+#endif
+
 constexpr int kBwdThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
 constexpr int kLdRow = 68;        // float2 slots per staged (lse, delta) block: 64 + 2 of alignment slack, padded
 constexpr int kInner = 64;  // rows per inner block
@@ -83,6 +92,7 @@ struct BwdParams {
   float scale_log2;
   int32_t* status;
   int out_width;         // absorb dX: columns written per row (= row stride of the output), <= D
+  long long* trace;
 };
 
 // kAbsorb = false: items x heads; outer/inner operands are per-head [rows, D] slices.
@@ -142,22 +152,33 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
   const int total = max(n_items, 0);  // one entry per head already
   int* const next_item = const_cast<int*>(&p.header->next_item);
   if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, kDKV ? 120 : 110, n_items);
+#ifdef VAFA_TRACE
+  long long tr[16];
+  for (int i = 0; i < 16; ++i) tr[i] = 0;
+  const long long t_begin = clock64();
+#endif
 
   if (warp == 8) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
       bool alive = true;
-      for (uint32_t n = 0; alive; ++n) {
-        const int idx = wq_produce(sm.wq, n, next_item, total, abort_flag);
-        if (idx < 0) break;
+      constexpr int kPrefetch = 6;  // inner blocks pulled into L2 ahead of their load (dU: X streams from HBM)
+      int idx = wq_produce(sm.wq, 0, next_item, total, abort_flag);
+      for (uint32_t n = 0; alive && idx >= 0; ++n) {
         const WorkItem w = p.items[idx];
         const int h = w.head;
         const int nb = (w.i_len + ib - 1) / ib;
-        if (nb == 0) continue;
+        if (nb == 0) {
+          idx = wq_produce(sm.wq, n + 1, next_item, total, abort_flag);
+          continue;
+        }
         constexpr bool kOneOuter = kAbsorb && kDKV;   // dX: the X tile is both outer operands
         constexpr bool kOneInner = kAbsorb && !kDKV;  // dU: the X block is both inner operands
-        if (!mbar_wait(smem_u32(&sm.outer_free), (qi & 1) ^ 1, abort_flag)) break;
+        if (kOneInner)
+          for (int b = 2; b < kPrefetch && b < nb; ++b)
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_inner_a, c * 64, h, w.i_start + b * ib);
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
         mbar_expect_tx(smem_u32(&sm.outer_full), (kOneOuter ? 1 : 2) * Cfg::kOuterBytes);
         for (int c = 0; c < Cfg::kSub; ++c) {
           tma_load_3d(smem_u32(sm.outer_a) + c * Cfg::kOuterSubBytes, &tmap_outer_a, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
@@ -168,7 +189,9 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * ib;
-          if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          if (kOneInner && b + kPrefetch < nb)
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_inner_a, c * 64, h, row + kPrefetch * ib);
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.in_full[st]), (kOneInner ? 1 : 2) * Cfg::kInnerBytes + (kDKV ? 66 * 8 : 0));
           if (kDKV) {
             // (lse, delta) pairs of the block's 64 inner columns: the copy starts at the even index
@@ -184,6 +207,17 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           }
         }
         ++qi;
+        // The next item is drawn now, while this one is being worked on, and its outer tile pulled into
+        // L2: the outer tiles are single-buffered, so their load is exposed once per item (dX has one
+        // inner block per item on user batches, and its X tile comes from HBM).
+        idx = alive ? wq_produce(sm.wq, n + 1, next_item, total, abort_flag) : -1;
+        if (idx >= 0) {
+          const WorkItem wn = p.items[idx];
+          for (int c = 0; c < Cfg::kSub; ++c) {
+            tma_prefetch_3d(&tmap_outer_a, c * 64, wn.head, wn.o_start);
+            if (!kOneOuter) tma_prefetch_3d(&tmap_outer_b, c * 64, wn.head, wn.o_start);
+          }
+        }
       }
     }
   } else if (warp == 9) {
@@ -198,7 +232,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       auto issue_xy = [&](uint32_t g, bool last) -> bool {
         const int st = g % S;
         const uint32_t ph = (g / S) & 1;
-        if (!mbar_wait(smem_u32(&sm.in_full[st]), ph, abort_flag)) return false;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.in_full[st]), ph, abort_flag)) return false; TRACE_ADD(4); }
         tc_fence_after();
         const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
         const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
@@ -229,7 +263,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         const WorkItem w = p.items[idx];
         const int nb = (w.i_len + ib - 1) / ib;
         if (nb == 0) continue;
-        if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
         tc_fence_after();
         if (!issue_xy(gk, nb == 1)) break;
         for (int b = 0; b < nb; ++b) {
@@ -238,7 +272,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             if (!issue_xy(g + 1, b + 2 == nb)) { alive = false; break; }
           }
           const int st = g % S;
-          if (!mbar_wait(smem_u32(&sm.ds_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.ds_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(7); }
           tc_fence_after();
           const uint32_t x_tmem = tbase + Cfg::kXCol + (g & 1) * kInner;
           const uint32_t y_tmem = tbase + Cfg::kYCol + (g & 1) * kInner;
@@ -299,8 +333,11 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
 
       for (int b = 0; b < nb; ++b) {
         const uint32_t g = gk + b;
-        if (!mbar_wait(smem_u32(&sm.xy_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.xy_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(8); }
         tc_fence_after();
+#ifdef VAFA_TRACE
+        const long long t_c0 = clock64();
+#endif
         const uint32_t x_addr = lane_base + Cfg::kXCol + (g & 1) * kInner;
         const uint32_t y_addr = lane_base + Cfg::kYCol + (g & 1) * kInner;
         // visibility of inner index jj = b*64 + i for this thread's outer row r
@@ -371,16 +408,24 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.ds_full[g & 1]));
+#ifdef VAFA_TRACE
+        tr[12] += clock64() - t_c0;
+        tr[11] += 1;
+#endif
       }
       if (!alive) break;
       gk += nb;
 
       // ---- epilogue ----
       if (nb > 0) {
-        if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break;
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break; TRACE_ADD(10); }
         tc_fence_after();
         ++qi;
       }
+#ifdef VAFA_TRACE
+      const long long t_e0 = clock64();
+      tr[14] += 1;
+#endif
       // output row: varlen (token, head); absorb dU stacked row (token*H + head); absorb dX key row
       const long long out_row = kAbsorb ? (kDKV ? (long long)w.o_start + r : (long long)w.o_start * p.H + r)
                                         : ((long long)w.o_start + r) * p.H + h;
@@ -403,23 +448,28 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
 #pragma unroll
             for (int i = 0; i < 32; ++i) t[i] = 0u;
           }
-          if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(optr + cc * 32);
+          uint32_t pw[16];
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]) * mul, __uint_as_float(t[8 * v4 + 1]) * mul);
-              u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * mul, __uint_as_float(t[8 * v4 + 3]) * mul);
-              u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * mul, __uint_as_float(t[8 * v4 + 5]) * mul);
-              u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * mul, __uint_as_float(t[8 * v4 + 7]) * mul);
-              if (cc * 32 + v4 * 8 < out_w) dst[v4] = u;
-            }
-          }
+          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
+          // consecutive tile rows are consecutive output rows in every mode of this template
+          const long long row_stride = kAbsorb ? (long long)out_w : (long long)p.H * D;
+          const int n_valid_rows = (kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows;
+          store_chunk_coalesced<T>(pw, optr + cc * 32, row_stride, r, n_valid_rows, min(4, max(0, (out_w - cc * 32) / 8)));
         }
       }
+#ifdef VAFA_TRACE
+      tr[13] += clock64() - t_e0;
+#endif
     }
   }
 
+#ifdef VAFA_TRACE
+  if (p.trace != nullptr && (threadIdx.x == 0 || threadIdx.x == 256 || threadIdx.x == 288)) {
+    tr[15] = clock64() - t_begin;
+    for (int i = 0; i < 16; ++i)
+      if (tr[i] != 0) p.trace[((long long)(kDKV ? 1 : 0) * 256 + blockIdx.x) * 16 + i] = tr[i];
+  }
+#endif
   // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
@@ -612,6 +662,12 @@ __global__ void __launch_bounds__(256) absorb_expand_wv_kernel(const T* __restri
   }
 }
 
+#ifdef VAFA_TRACE
+}  // namespace
+long long* vafa_trace_buffer_abs = nullptr;
+namespace {
+#endif
+
 struct AbsorbBwdWs {
   size_t hdr_du, hdr_dx, items_du, items_dx, total;
   int cap_du, cap_dx;
@@ -657,6 +713,16 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   BwdParams p;
   p.ld = (const float2*)a.ld; p.ld_stride = 0; p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
   p.out_width = a.x_width;
+  p.trace = nullptr;
+#ifdef VAFA_TRACE
+  {
+    static long long* g_trace = nullptr;  // debugging aid only
+    if (!g_trace) cudaMalloc(&g_trace, 512 * 16 * sizeof(long long));
+    cudaMemsetAsync(g_trace, 0, 512 * 16 * sizeof(long long), s);
+    p.trace = g_trace;
+    vafa_trace_buffer_abs = g_trace;
+  }
+#endif
   p.out1 = nullptr;
   {
     p.out0 = a.du; p.header = sq.header; p.items = sq.items;
@@ -730,3 +796,10 @@ int sm100_varlen_bwd(const vafa_varlen_args* a, cudaStream_t s) {
 }
 
 }  // namespace vafa
+
+#ifdef VAFA_TRACE
+extern "C" __attribute__((visibility("default"))) int vafa_trace_read_abs(long long* host, int n) {
+  if (!vafa::vafa_trace_buffer_abs) return -1;
+  return (int)cudaMemcpy(host, vafa::vafa_trace_buffer_abs, (size_t)n * 16 * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+#endif

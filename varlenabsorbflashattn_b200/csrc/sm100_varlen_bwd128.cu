@@ -478,18 +478,10 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 #pragma unroll
             for (int i = 0; i < 32; ++i) t[i] = 0u;
           }
-          if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(optr + cc * 32);
+          uint32_t pw[16];
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]) * mul, __uint_as_float(t[8 * v4 + 1]) * mul);
-              u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * mul, __uint_as_float(t[8 * v4 + 3]) * mul);
-              u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * mul, __uint_as_float(t[8 * v4 + 5]) * mul);
-              u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * mul, __uint_as_float(t[8 * v4 + 7]) * mul);
-              dst[v4] = u;
-            }
-          }
+          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
+          store_chunk_coalesced<T>(pw, optr + cc * 32, (long long)p.H * D, r, w.o_rows, 4);
         }
       }
     }

@@ -165,10 +165,20 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         mbar_expect_tx(smem_u32(&sm.q_full), Cfg::kTileBytes);
         for (int c = 0; c < Cfg::kSub; ++c)
           tma_load_3d(smem_u32(sm.q) + c * Cfg::kSubBytes, &tmap_q, smem_u32(&sm.q_full), c * 64, h, w.o_start);
+        // absorb: X is streamed once from HBM (no other CTA reads this user's keys), and a K slot is only
+        // released after P.X of its block, so the two-slot ring alone leaves the HBM latency exposed
+        // (measured: the MMA issuer waited for tiles half of the time).  Tiles a few blocks ahead are
+        // therefore pulled into L2 first.
+        constexpr int kPrefetch = 4;
+        if (kAbsorb)
+          for (int b = 2; b < kPrefetch && b < nb; ++b)
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, w.i_start + b * kTile);
         for (int b = 0; b < nb; ++b, ++gk) {
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * kTile;
+          if (kAbsorb && b + kPrefetch < nb)
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, row + kPrefetch * kTile);
           // slot free: S(gk-2) complete (absorb: P.X(gk-2) complete, the tile doubles as V)
           { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.o_done[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
@@ -413,18 +423,13 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #pragma unroll
             for (int i = 0; i < 32; ++i) t[i] = 0u;
           }
-          if (row_ok) {
-            uint4* dst = reinterpret_cast<uint4*>(optr + cc * 32);
+          uint32_t pw[16];
 #pragma unroll
-            for (int v4 = 0; v4 < 4; ++v4) {
-              uint4 u;
-              u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]) * inv_l, __uint_as_float(t[8 * v4 + 1]) * inv_l);
-              u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]) * inv_l, __uint_as_float(t[8 * v4 + 3]) * inv_l);
-              u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]) * inv_l, __uint_as_float(t[8 * v4 + 5]) * inv_l);
-              u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]) * inv_l, __uint_as_float(t[8 * v4 + 7]) * inv_l);
-              dst[v4] = u;
-            }
-          }
+          for (int i = 0; i < 16; ++i)
+            pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * inv_l, __uint_as_float(t[2 * i + 1]) * inv_l);
+          // rows of the tile are consecutive (token, head) rows of O: H*D apart (absorb: D apart)
+          store_chunk_coalesced<T>(pw, optr + cc * 32, kAbsorb ? (long long)D : (long long)p.H * D, r,
+                                   kAbsorb ? w.o_rows * p.H : w.o_rows, 4);
         }
         if (row_ok && half == 0) p.lse[row * p.H + h] = lse_val;
       } else {
@@ -672,6 +677,15 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.trace = nullptr;
+#ifdef VAFA_TRACE
+  {
+    static long long* g_trace_a = nullptr;  // debugging aid only: leaked on purpose
+    if (!g_trace_a) cudaMalloc(&g_trace_a, 1024 * 16 * sizeof(long long));
+    cudaMemsetAsync(g_trace_a, 0, 1024 * 16 * sizeof(long long), s);
+    p.trace = g_trace_a;
+    vafa_trace_buffer = g_trace_a;
+  }
+#endif
   const size_t smem = sizeof(FwdSmem<D, true>) + 1024;
   VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   LaunchScope scope(kKAbsorbFwd, s);
