@@ -42,9 +42,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # exists for this workload.
 NCU_TRAFFIC_BYTES = {
     # profiles/varlen_kernels_C2_ncu_full.md (dram__bytes_read.sum + dram__bytes_write.sum, one launch)
-    ("C2", "varlen_bwd_kernel<dKV>"): 570_584_832 + 227_940_864,
-    ("C2", "varlen_bwd_kernel<dQ>"): 539_180_544 + 112_521_728,
-    ("C2", "varlen_fwd_kernel"): 399_229_696 + 110_594_816,
+    ("C2", "varlen_bwd_kernel<dKV>"): 574_531_328 + 231_917_056,
+    ("C2", "varlen_bwd_kernel<dQ>"): 540_098_816 + 116_789_504,
+    ("C2", "varlen_fwd_kernel"): 400_167_424 + 113_049_344,
 }
 
 
