@@ -61,16 +61,23 @@ struct BwdCfg {
 
 // kAbsorb (the absorb operator, D = d_kv = 256): keys and values are the same X rows, so the dU
 // kernel has one inner operand and the dX kernel one outer operand; the unused buffer shrinks.
+// Ring depth.  The absorb dU kernel streams X from HBM and releases a block only after its second use
+// (dU += dS X), while the next score product is issued one block ahead: with two stages that product
+// always waited a full load; its unused inner_b and (lse, delta) staging shrink to make room for three.
+template <int D, bool kDKV, bool kAbsorb>
+constexpr int bwd_stages() { return (D == 256 && kAbsorb && !kDKV) ? 3 : BwdCfg<D>::kStages; }
+
 template <int D, bool kDKV = false, bool kAbsorb = false>
 struct BwdSmem {
+  static constexpr int kS = bwd_stages<D, kDKV, kAbsorb>();
   alignas(1024) uint8_t outer_a[BwdCfg<D>::kOuterBytes];
   alignas(1024) uint8_t outer_b[(kAbsorb && kDKV) ? 1024 : BwdCfg<D>::kOuterBytes];
-  alignas(1024) uint8_t inner_a[BwdCfg<D>::kStages][BwdCfg<D>::kInnerBytes];
-  alignas(1024) uint8_t inner_b[BwdCfg<D>::kStages][(kAbsorb && !kDKV) ? 1024 : BwdCfg<D>::kInnerBytes];
+  alignas(1024) uint8_t inner_a[kS][BwdCfg<D>::kInnerBytes];
+  alignas(1024) uint8_t inner_b[kS][(kAbsorb && !kDKV) ? 16 : BwdCfg<D>::kInnerBytes];
   alignas(8) uint64_t outer_full, outer_free;
-  uint64_t in_full[BwdCfg<D>::kStages], in_empty[BwdCfg<D>::kStages];
+  uint64_t in_full[kS], in_empty[kS];
   uint64_t xy_full[2], ds_full[2], acc_done;
-  alignas(16) float2 ld[BwdCfg<D>::kStages][kLdRow];  // dKV: (lse, delta) of the inner block's query rows
+  alignas(16) float2 ld[kS][kDKV ? kLdRow : 2];  // dKV: (lse, delta) of the inner block's query rows
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
@@ -108,9 +115,9 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
                   const __grid_constant__ CUtensorMap tmap_inner_a, const __grid_constant__ CUtensorMap tmap_inner_b,
                   const BwdParams p) {
   using Cfg = BwdCfg<D>;
-  constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   using Smem = BwdSmem<D, kDKV, kAbsorb>;
+  constexpr int S = Smem::kS;
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sm.abort_flag;
