@@ -102,6 +102,9 @@ struct BwdParams {
   long long* trace;
 };
 
+// Only the absorb forms (kAbsorb = true, D = 256) are launched: packed_varlen_attn's dQ and dK/dV run on
+// the 128 x 128-tile kernels of sm100_varlen_bwd128.cu, which replaced the kAbsorb = false form of this
+// template (kept because the two forms share every line but the operand bookkeeping).
 // kAbsorb = false: items x heads; outer/inner operands are per-head [rows, D] slices.
 // kAbsorb = true : heads are stacked into the tile rows (row = q*H + h) exactly as in the forward;
 //   dU kernel (kDKV = false): outer = (U, dAlphaX) stacked rows of 128/H queries, inner = X blocks,
