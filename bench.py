@@ -180,7 +180,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "varlen-attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: packed varlen causal attention fwd+bwd, H={cfg['H']} D={cfg['D']}",
+        "config": {"workload": f"{args.workload}: packed varlen {'causal' if cfg['causal'] else 'non-causal'} attention fwd+bwd, H={cfg['H']} D={cfg['D']}",
                    "note": "reference's torch CPU path (per-segment fp32 matmul-softmax-matmul, autograd backward); each step is a bounded sample"},
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -447,10 +447,10 @@ def main():
             "metric": "varlen-attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: packed varlen causal attention fwd+bwd, {len(ql)} sequences/rank, "
+            "config": {"workload": f"{args.workload}: packed varlen {'causal' if causal else 'non-causal'} attention fwd+bwd, {len(ql)} sequences/rank, "
                                    f"{sum(ql)} tokens/rank, H={H} D={D} bf16",
-                       "flops_convention": "fwd 4*H*D*cells (causal cells), bwd 2.5x fwd",
-                       "l2": "inputs larger than L2 (q,k,v,dO,o,dq,dk,dv: 8 x %.0f MB)" % (hq.numel() * 2 / 1e6),
+                       "flops_convention": "fwd 4*H*D*cells (visible cells), bwd 2.5x fwd",
+                       "l2": "inputs larger than L2 (q, dO, o, dq: %.0f MB each; k, v, dk, dv: %.0f MB each)" % (hq.numel() * 2 / 1e6, hk.numel() * 2 / 1e6),
                        "parallelism": f"dp{world} by sequence, no data-path collective"},
             "fwd_only": {"value": fwd_value, "unit": "TFLOP/s", "ms": ms_fwd},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "sequence_groups": len(groups),

@@ -59,6 +59,11 @@ CONFIGS: Dict[str, dict] = {
     "C4": dict(kind="absorb", H=8, D_H=32, d_q=256, d_kv=256, dtype="bf16"),
     "C5v": dict(kind="varlen", H=32, D=128, dtype="bf16", causal=True),
     "C5a": dict(kind="absorb", H=8, D_H=32, d_q=256, d_kv=256, dtype="bf16"),
+    # production-like training shape of the varlen operator: few users, 500 queries each, very long key
+    # histories (the reference's fixture of 958 logged batches, triton_fa_varlen_v2/fixtures/
+    # stage1_shapes.jsonl: 16-30 users, q = 500, k up to 102 400 with more than half of the users at the
+    # cap; its harness defaults to 4 heads of 64, tools/benchmark_packed_varlen_flash_attn.py:1497-1498)
+    "S1": dict(kind="varlen", H=4, D=64, dtype="bf16", causal=False),
 }
 
 
@@ -80,6 +85,12 @@ def config_lengths(name: str, seed: int = 0) -> Tuple[List[int], List[int]]:
     if name == "C5v":
         L = log_uniform_until(1_000_000, 128, 8192, seed)
         return L, list(L)
+    if name == "S1":
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        n = 23
+        capped = torch.rand(n, generator=g, dtype=torch.float64) < 0.55
+        tail = log_uniform_lengths(n, 1, 102400, seed + 1)
+        return [500] * n, [102400 if c else t for c, t in zip(capped.tolist(), tail)]
     if name == "C5a":
         return uniform_lengths(16384, 1, 16, seed), log_uniform_lengths(16384, 8, 2048, seed + 1)
     raise KeyError(name)
