@@ -70,3 +70,24 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.load()
+
+
+def test_absorb_narrow_x_needs_a_valid_width(lib):
+    """x_width (rows of x / dx narrower than d_kv) must be a multiple of 8 and at most d_kv; the check runs
+    before anything touches the device."""
+    a = _lib.AbsorbArgs()
+    a.n_seg, a.total_q, a.total_k, a.num_heads, a.head_dim, a.dtype = 1, 0, 0, 8, 32, 1
+    a.d_q, a.d_kv = 256, 256
+    cu = (C.c_int32 * 2)(0, 0)
+    a.cu_seqlens_q = a.cu_seqlens_k = C.cast(cu, C.c_void_p)
+    dummy = (C.c_char * 64)()
+    a.w_q = a.w_k = a.w_v = C.cast(dummy, C.c_void_p)
+    a.x_width = 300
+    assert lib.vafa_absorb_fwd(C.byref(a), None) == -1
+    assert b"x_width" in lib.vafa_last_error()
+    a.x_width = 212
+    assert lib.vafa_absorb_fwd(C.byref(a), None) == -1
+    # a valid narrow width without the tensor-core path (nothing to attend over here) is refused as unsupported
+    a.x_width = 216
+    assert lib.vafa_absorb_fwd(C.byref(a), None) == -2
+    assert b"tcgen05" in lib.vafa_last_error()
