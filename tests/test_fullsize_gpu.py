@@ -142,3 +142,30 @@ def test_config4_absorb_quarter_against_oracle():
     assert torch.equal(O, O2)
     for a, b in zip(g, g2):
         assert torch.equal(a.grad, b.grad)
+
+
+def test_config5_varlen_full_size_properties():
+    """The whole 1 M-token configuration 5 batch (520 sequences, H=32, D=128, causal): 4.1e9 elements per
+    tensor, so every offset past 2^31 elements is exercised.  Needs about 70 GB on the device."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 90 * 2**30:
+        pytest.skip("needs about 70 GB of free device memory")
+    V.set_impl("auto")
+    ql, _ = config_lengths("C5v")
+    T, H, D = sum(ql), 32, 128
+    cu = lengths_to_cu(ql).to(DEV)
+    q, k, do = _randn((T, H, D), 1), _randn((T, H, D), 2), _randn((T, H, D), 4)
+    ones = torch.ones((T, H, D), device=DEV, dtype=torch.bfloat16)
+    qg, kg, vg = q.requires_grad_(True), k.requires_grad_(True), ones.requires_grad_(True)
+    o = vb.packed_varlen_attn(qg, kg, vg, cu_seqlens_q=cu, cu_seqlens_k=cu, causal=True)
+    assert (o.float() - 1.0).abs().max().item() <= 8e-3
+    o.backward(do)
+    del o
+    assert qg.grad.float().abs().max().item() <= 3e-2 and kg.grad.float().abs().max().item() <= 3e-2
+    st = _starts(ql)
+    for s in (0, len(ql) // 2, len(ql) - 1):  # the last sequence sits at the largest offsets
+        a = vg.grad[st[s]:st[s] + ql[s]].float().sum(0)
+        b = do[st[s]:st[s] + ql[s]].float().sum(0)
+        assert (a - b).abs().max().item() <= 2e-2 * max(1.0, b.abs().max().item())
+    del qg, kg, vg, q, k, do, ones
+    torch.cuda.empty_cache()
