@@ -143,15 +143,26 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   int G = 1;
   while (G < 32 && G * p.n_seg < kSchedThreads) G <<= 1;
 
-  // pass 1: totals
+  // pass 1: totals, and the cost histogram for the common case that nothing is split (one item per
+  // tile); only a list that does get split goes through passes 2 and 3
   {
     int units = 0;
     long long blocks = 0;
     for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
+      long long cost = 0;
+      int items = 0;
       for (int t = t0; t < g.n_tiles; t += ts) {
         const Unit u = make_unit(p, g, t);
-        if (u.i_len > 0) { units += 1; blocks += n_blocks(u.i_len); }
+        const int nb = n_blocks(u.i_len);
+        if (u.i_len > 0) { units += 1; blocks += nb; }
+        cost += nb;
+        items += 1;
       }
+      for (int o = ts >> 1; o > 0; o >>= 1) {
+        cost += __shfl_xor_sync(0xffffffffu, cost, o);
+        items += __shfl_xor_sync(0xffffffffu, items, o);
+      }
+      warp_hist_add(s_hist, t0 == 0 && items > 0, cost_bucket(cost), items * p.H);
     });
     units = (int)warp_sum_ll(units);
     blocks = warp_sum_ll(blocks);
@@ -177,8 +188,13 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   }
   __syncthreads();
 
+  const bool any_split = s_bs != 0;
+  if (any_split) {
+    for (int b = threadIdx.x; b < kBuckets; b += kSchedThreads) s_hist[b] = 0;
+    __syncthreads();
+  }
   // pass 2: make the split fit the capacities (double the slice until it does)
-  for (int round = 0; round < 24; ++round) {
+  for (int round = 0; any_split && round < 24; ++round) {
     if (threadIdx.x == 0) { s_items = 0; s_rows = 0; }
     __syncthreads();
     const int bs = s_bs;
@@ -205,7 +221,7 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   const int bs = s_bs;
 
   // pass 3: items per cost bucket of their segment
-  for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
+  if (any_split) for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
     long long cost = 0;
     int items = 0;
     for (int t = t0; t < g.n_tiles; t += ts) {
