@@ -62,6 +62,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Waits until either barrier has completed its phase: 1 = the first one is ready (checked first),
+// 2 = only the second one, 0 = the bounded wait ran out or another role gave up.
+__device__ __forceinline__ int mbar_wait_either(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
+                                                volatile int* abort_flag) {
+  const long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar_a, parity_a)) return 1;
+    if (mbar_try_wait(bar_b, parity_b)) return 2;
+    if ((++spins & 63u) == 0u) {
+      if (*abort_flag != 0) return 0;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return 0;
+      }
+    }
+  }
+}
+
 // ---- TMA --------------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -267,19 +267,38 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         return true;
       };
 
-      for (uint32_t n = 0; alive; ++n) {
-        const int idx = wq_consume_thread(sm.wq, n, abort_flag);
-        if (idx < 0) break;
-        const WorkItem w = p.items[idx];
-        const int nb = (w.i_len + ib - 1) / ib;
-        if (nb == 0) continue;
-        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
+      // Items are walked with a lookahead of one block across item boundaries: the score products of the
+      // next item's first block are issued before the last accumulate products of this item, which wait
+      // for the element-wise warps (absorb dX has one block per item: without the lookahead its score
+      // products, element-wise phase, accumulate products and epilogue ran back to back).
+      uint32_t n_next = 0;
+      int nb_next = 0;
+      // draws items until one has inner blocks; waits for its outer tile and issues its first score products
+      auto start_next_item = [&]() -> bool {
+        while (true) {
+          const int idx = wq_consume_thread(sm.wq, n_next++, abort_flag);
+          if (idx < 0) return false;
+          const WorkItem w = p.items[idx];
+          nb_next = (w.i_len + ib - 1) / ib;
+          if (nb_next > 0) break;
+        }
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) return false; TRACE_ADD(3); }
         tc_fence_after();
-        if (!issue_xy(gk, nb == 1)) break;
+        ++qi;
+        return issue_xy(gk, nb_next == 1);
+      };
+      bool have = start_next_item();
+      while (have && alive) {
+        const int nb = nb_next;
+        const uint32_t g0 = gk;
+        gk += nb;  // start_next_item() issues block gk
+        have = false;
         for (int b = 0; b < nb; ++b) {
-          const uint32_t g = gk + b;
+          const uint32_t g = g0 + b;
           if (b + 1 < nb) {
             if (!issue_xy(g + 1, b + 2 == nb)) { alive = false; break; }
+          } else {
+            have = start_next_item();
           }
           const int st = g % S;
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.ds_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(7); }
@@ -309,8 +328,6 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           mma_commit(smem_u32(&sm.in_empty[st]));
           if (b + 1 == nb) mma_commit(smem_u32(&sm.acc_done));
         }
-        gk += nb;
-        ++qi;
       }
     }
   } else {
@@ -323,6 +340,56 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
     const float c = p.scale_log2;
     uint32_t gk = 0, qi = 0;
     bool alive = true;
+    // ---- epilogue of one item: accumulator (nb > 0) or zeros -> global memory ----
+    auto epilogue = [&](const WorkItem& w, int nb) -> bool {
+      const int h = w.head;
+      if (nb > 0) {
+        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) return false; TRACE_ADD(10); }
+        tc_fence_after();
+        ++qi;
+      }
+#ifdef VAFA_TRACE
+      const long long t_e0 = clock64();
+      tr[14] += 1;
+#endif
+      // output row: varlen (token, head); absorb dU stacked row (token*H + head); absorb dX key row
+      const long long out_row = kAbsorb ? (kDKV ? (long long)w.o_start + r : (long long)w.o_start * p.H + r)
+                                        : ((long long)w.o_start + r) * p.H + h;
+      // absorb dX rows are out_width wide (the caller's X may be narrower than the 256-column tile)
+      const int out_w = (kAbsorb && kDKV) ? p.out_width : D;
+#pragma unroll
+      for (int which = 0; which < ((kDKV && !kAbsorb) ? 2 : 1); ++which) {
+        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * out_w;
+        // dV unscaled; dQ, dK and dU scaled here; absorb dX carries the scale inside dS
+        const float mul = (kDKV && (which == 0)) ? 1.f : p.scale;
+        const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
+#pragma unroll
+        for (int c2 = 0; c2 < D / 64; ++c2) {
+          const int cc = half * (D / 64) + c2;  // each half of the compute warps writes half of the columns
+          uint32_t t[32];
+          if (nb > 0) {
+            tmem_ld32(lane_base + acc_col + cc * 32, t);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) t[i] = 0u;
+          }
+          uint32_t pw[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
+          // consecutive tile rows are consecutive output rows in every mode of this template
+          const long long row_stride = kAbsorb ? (long long)out_w : (long long)p.H * D;
+          const int n_valid_rows = (kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows;
+          store_chunk_coalesced<T>(pw, optr + cc * 32, row_stride, r, n_valid_rows, min(4, max(0, (out_w - cc * 32) / 8)));
+        }
+      }
+#ifdef VAFA_TRACE
+      tr[13] += clock64() - t_e0;
+#endif
+      return true;
+    };
+    bool pend = false;
+    WorkItem pend_w;
     for (uint32_t n = 0; alive; ++n) {
       const int idx = wq_consume_warp(sm.wq, n, abort_flag);
       if (idx < 0) break;
@@ -416,6 +483,14 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
         };
         if (__any_sync(0xffffffffu, need_mask)) block_body(std::true_type{}); else block_body(std::false_type{});
         tmem_wait_st();
+        // The previous item's accumulator is read back here, after this item's first block has been
+        // through the element-wise phase and before its products are released (they overwrite the
+        // accumulator): the wait for the last accumulate products of an item then runs under the next
+        // item's element-wise work instead of stalling these warps (absorb dX: one block per item).
+        if (pend) {
+          pend = false;
+          if (!epilogue(pend_w, 1)) { alive = false; break; }
+        }
         tc_fence_before();
         mbar_arrive(smem_u32(&sm.ds_full[g & 1]));
 #ifdef VAFA_TRACE
@@ -426,51 +501,16 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
       if (!alive) break;
       gk += nb;
 
-      // ---- epilogue ----
+      // The accumulator is read back only after the first block of the next item has been through the
+      // element-wise phase (see there); an item without inner rows writes its zeros at once.
       if (nb > 0) {
-        { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.acc_done), qi & 1, abort_flag)) break; TRACE_ADD(10); }
-        tc_fence_after();
-        ++qi;
+        pend = true;
+        pend_w = w;
+      } else {
+        epilogue(w, 0);
       }
-#ifdef VAFA_TRACE
-      const long long t_e0 = clock64();
-      tr[14] += 1;
-#endif
-      // output row: varlen (token, head); absorb dU stacked row (token*H + head); absorb dX key row
-      const long long out_row = kAbsorb ? (kDKV ? (long long)w.o_start + r : (long long)w.o_start * p.H + r)
-                                        : ((long long)w.o_start + r) * p.H + h;
-#pragma unroll
-      // absorb dX rows are out_width wide (the caller's X may be narrower than the 256-column tile)
-      const int out_w = (kAbsorb && kDKV) ? p.out_width : D;
-      for (int which = 0; which < ((kDKV && !kAbsorb) ? 2 : 1); ++which) {
-        T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * out_w;
-        // dV unscaled; dQ, dK and dU scaled here; absorb dX carries the scale inside dS
-        const float mul = (kDKV && (which == 0)) ? 1.f : p.scale;
-        const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
-#pragma unroll
-        for (int c2 = 0; c2 < D / 64; ++c2) {
-          const int cc = half * (D / 64) + c2;  // each half of the compute warps writes half of the columns
-          uint32_t t[32];
-          if (nb > 0) {
-            tmem_ld32(lane_base + acc_col + cc * 32, t);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) t[i] = 0u;
-          }
-          uint32_t pw[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
-          // consecutive tile rows are consecutive output rows in every mode of this template
-          const long long row_stride = kAbsorb ? (long long)out_w : (long long)p.H * D;
-          const int n_valid_rows = (kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows;
-          store_chunk_coalesced<T>(pw, optr + cc * 32, row_stride, r, n_valid_rows, min(4, max(0, (out_w - cc * 32) / 8)));
-        }
-      }
-#ifdef VAFA_TRACE
-      tr[13] += clock64() - t_e0;
-#endif
     }
+    if (alive && pend) epilogue(pend_w, 1);
   }
 
 #ifdef VAFA_TRACE

@@ -232,11 +232,25 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (!issue_qk(gk, nb == 1)) break;
         for (int b = 0; b < nb; ++b) {
           const uint32_t g = gk + b;
-          if (b + 1 < nb) {
-            if (!issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
-          }
           const int st = g % S;
           const uint32_t ph = (g / S) & 1;
+          bool qk_pending = b + 1 < nb, qk_first = true;
+          if (kAbsorb && qk_pending) {
+            // The X tile of block g+1 is only requested once P.X of block g-1 has released its slot, so it
+            // can still be on its way when P of block g is ready.  Waiting for it here would put the load
+            // latency in series with both products of every block (measured: half of this thread's time):
+            // the product whose operands are there first is issued first.
+            TRACE_T0();
+            const int first = mbar_wait_either(smem_u32(&sm.k_full[(g + 1) % S]), ((g + 1) / S) & 1,
+                                               smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag);
+            TRACE_ADD(7);
+            if (first == 0) { alive = false; break; }
+            qk_first = first == 1;
+          }
+          if (qk_pending && qk_first) {
+            if (!issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
+            qk_pending = false;
+          }
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.p_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(5); }
           if (!kAbsorb) { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
           tc_fence_after();
@@ -248,6 +262,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, v_lo + kk * (2048 >> 4), idesc_pv,
                     (b > 0 || kk > 0) ? 1u : 0u);
           mma_commit(smem_u32(&sm.o_done[g & 1]));
+          if (qk_pending && !issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
         }
         gk += nb;
         ++qi;
