@@ -149,3 +149,34 @@ def test_validation_raises_on_gpu_inputs():
     d = [t.to(DEV) for t in (q_raw, X, W_Q, W_K, W_V)]
     with pytest.raises(ValueError, match="k_len > 0"):
         vb.packed_target_attn(*d, cu_seqlens_q=cu_q, cu_seqlens_k=torch.tensor([0, 9, 9], dtype=torch.int32))
+
+
+def test_forward_backward_inside_a_cuda_graph():
+    """The call forks a library-owned side stream for the tile-list builder and rejoins it before it
+    returns, which must be legal inside a stream capture: a captured forward+backward replays to the
+    same bits as the eager call."""
+    ql = uniform_lengths(40, 1, 16, 0)
+    kl = log_uniform_lengths(40, 8, 600, 1)
+    ins = make_absorb_inputs(ql, kl, 256, 256, 8, 32, torch.bfloat16, 0, x_std=1.0, w_std=None)
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = ins
+    g = [t.to(DEV).requires_grad_(True) for t in (q_raw, X, W_Q, W_K, W_V)]
+    cu_q, cu_k, dO = cu_q.to(DEV), cu_k.to(DEV), dO.to(DEV)
+
+    def step():
+        O = vb.packed_target_attn(*g, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, validate=False)
+        return (O,) + torch.autograd.grad(O, g, dO)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            eager = [t.clone() for t in step()]
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = step()
+    for _ in range(2):
+        graph.replay()
+    torch.cuda.synchronize()
+    for name, a, b in zip(("O", "dq_raw", "dX", "dW_Q", "dW_K", "dW_V"), captured, eager):
+        assert torch.equal(a, b), name

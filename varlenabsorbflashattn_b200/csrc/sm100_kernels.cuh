@@ -45,6 +45,7 @@ struct AbsorbCoreArgs {
   void* workspace;
   int32_t* status;
   int x_width;
+  int lists_built;     // the tile list was already built by sm100_absorb_core_fwd_lists() (ordered before this call)
 };
 size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H);
 int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s);
@@ -61,9 +62,14 @@ struct AbsorbCoreBwdArgs {
   void* workspace;
   int32_t* status;
   int x_width;         // row width of x and dx (<= 256)
+  int lists_built;     // the tile lists were already built by sm100_absorb_core_bwd_lists()
 };
 size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H);
 int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);
+// The tile lists depend on cu_seqlens only: these build them on their own (on any stream the caller
+// orders before the core call), so that the single-CTA list builder runs beside the projections.
+int sm100_absorb_core_fwd_lists(const AbsorbCoreArgs& a, cudaStream_t s);
+int sm100_absorb_core_bwd_lists(const AbsorbCoreBwdArgs& a, cudaStream_t s);
 int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s);
 int sm100_absorb_expand_wv(const void* w_v, void* bexp, int H, int D_H, int d_kv, int dtype, cudaStream_t s);
 

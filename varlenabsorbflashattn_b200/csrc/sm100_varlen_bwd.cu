@@ -735,22 +735,35 @@ AbsorbBwdWs absorb_bwd_ws(int total_q, int total_k, int n_seg, int H) {
   return w;
 }
 
-template <typename T>
-int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
-  constexpr int D = 256;
-  const int sms = resolve_sm_count_bwd(a.sm_count);
+struct AbsorbBwdSched {
+  SchedParams du, dx;
+};
+
+AbsorbBwdSched absorb_bwd_sched_params(const AbsorbCoreBwdArgs& a, int sms) {
   const AbsorbBwdWs ws = absorb_bwd_ws(a.total_q, a.total_k, a.n_seg, a.H);
   char* base = (char*)a.workspace;
-  int rc;
-  SchedParams sq;
+  AbsorbBwdSched r;
+  SchedParams& sq = r.du;
   sq.cu_q = a.cu_q; sq.cu_k = a.cu_k; sq.n_seg = a.n_seg; sq.mode = kSchedDq; sq.causal = 0; sq.H = 1;
   sq.sm_count = sms; sq.split_len = 0; sq.tile_rows = kTile / a.H;
   sq.cap_items = ws.cap_du; sq.cap_combine = 0; sq.cap_rows = 0;
   sq.header = (SchedHeader*)(base + ws.hdr_du); sq.items = (WorkItem*)(base + ws.items_du); sq.combine = nullptr;
-  SchedParams sk = sq;
+  r.dx = sq;
+  SchedParams& sk = r.dx;
   sk.mode = kSchedDkv; sk.tile_rows = kTile; sk.cap_items = ws.cap_dx;
   sk.header = (SchedHeader*)(base + ws.hdr_dx); sk.items = (WorkItem*)(base + ws.items_dx);
-  if ((rc = launch_scheduler_pair(sq, sk, s))) return rc;
+  return r;
+}
+
+template <typename T>
+int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
+  constexpr int D = 256;
+  const int sms = resolve_sm_count_bwd(a.sm_count);
+  const AbsorbBwdSched sch = absorb_bwd_sched_params(a, sms);
+  const SchedParams& sq = sch.du;
+  const SchedParams& sk = sch.dx;
+  int rc;
+  if (!a.lists_built && (rc = launch_scheduler_pair(sq, sk, s))) return rc;
 
   CUtensorMap u128, g128, x64, x128, u64, g64;
   if ((rc = encode_tmap_rows(&u128, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
@@ -797,6 +810,11 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
 
 size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H) {
   return absorb_bwd_ws(total_q, total_k, n_seg, H).total;
+}
+
+int sm100_absorb_core_bwd_lists(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
+  const AbsorbBwdSched sch = absorb_bwd_sched_params(a, resolve_sm_count_bwd(a.sm_count));
+  return launch_scheduler_pair(sch.du, sch.dx, s);
 }
 
 int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {

@@ -668,10 +668,7 @@ AbsorbCoreWs absorb_core_ws(int total_q, int n_seg, int H) {
   return w;
 }
 
-template <typename T>
-int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
-  constexpr int D = 256;
-  const int sms = resolve_sm_count(a.sm_count);
+SchedParams absorb_fwd_sched_params(const AbsorbCoreArgs& a, int sms) {
   const AbsorbCoreWs ws = absorb_core_ws(a.total_q, a.n_seg, a.H);
   char* base = (char*)a.workspace;
   SchedParams sp;
@@ -681,7 +678,15 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   sp.header = (SchedHeader*)(base + ws.header);
   sp.items = (WorkItem*)(base + ws.items);
   sp.combine = nullptr;
-  int rc = launch_scheduler(sp, s);
+  return sp;
+}
+
+template <typename T>
+int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
+  constexpr int D = 256;
+  const int sms = resolve_sm_count(a.sm_count);
+  const SchedParams sp = absorb_fwd_sched_params(a, sms);
+  int rc = a.lists_built ? 0 : launch_scheduler(sp, s);
   if (rc) return rc;
   CUtensorMap tu, tx;
   if ((rc = encode_tmap_rows(&tu, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
@@ -712,6 +717,10 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
 }  // namespace
 
 size_t sm100_absorb_core_fwd_workspace_bytes(int total_q, int n_seg, int H) { return absorb_core_ws(total_q, n_seg, H).total; }
+
+int sm100_absorb_core_fwd_lists(const AbsorbCoreArgs& a, cudaStream_t s) {
+  return launch_scheduler(absorb_fwd_sched_params(a, resolve_sm_count(a.sm_count)), s);
+}
 
 int sm100_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   return a.dtype == VAFA_BF16 ? launch_absorb_core_fwd<__nv_bfloat16>(a, s) : launch_absorb_core_fwd<__half>(a, s);

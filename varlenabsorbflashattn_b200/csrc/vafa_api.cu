@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
@@ -162,6 +163,66 @@ AbsorbFast absorb_fast(const vafa_absorb_args* a, bool inner) {
   return f;
 }
 
+// A second stream per device for the tile-list builders of the absorb operator.  The lists depend on
+// cu_seqlens only and their builder is latency-bound on one or two SMs, so it runs beside the
+// projections instead of in front of the attention kernels: fork() orders the side stream after
+// everything already queued on the caller's stream, join() orders the caller's stream after the side
+// stream.  Both are event waits (legal inside a stream capture, where the side stream joins the capture
+// and is rejoined before the call returns).  Created on first use; no device memory is allocated.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t forked = nullptr, joined = nullptr;
+};
+constexpr int kMaxSideDevices = 64;
+std::mutex g_side_mu;
+SideStream g_side[kMaxSideDevices];
+
+int side_fork(cudaStream_t s, SideStream** out) {
+  int dev = -1;
+  VAFA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxSideDevices) return fail(VAFA_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_side_mu);
+  SideStream& ss = g_side[dev];
+  if (ss.stream == nullptr) {
+    VAFA_CUDA_CHECK(cudaStreamCreateWithFlags(&ss.stream, cudaStreamNonBlocking));
+    VAFA_CUDA_CHECK(cudaEventCreateWithFlags(&ss.forked, cudaEventDisableTiming));
+    VAFA_CUDA_CHECK(cudaEventCreateWithFlags(&ss.joined, cudaEventDisableTiming));
+  }
+  // record and wait under one lock: a wait refers to the latest record of its event
+  VAFA_CUDA_CHECK(cudaEventRecord(ss.forked, s));
+  VAFA_CUDA_CHECK(cudaStreamWaitEvent(ss.stream, ss.forked, 0));
+  *out = &ss;
+  return 0;
+}
+
+// Marks the end of this call's work on the side stream.  The later wait may see a newer record of the
+// same event (another call's): the side stream runs in order, so that one is behind this call's work too.
+int side_done(SideStream* ss) {
+  std::lock_guard<std::mutex> lk(g_side_mu);
+  VAFA_CUDA_CHECK(cudaEventRecord(ss->joined, ss->stream));
+  return 0;
+}
+
+int side_join(cudaStream_t s, SideStream* ss) {
+  std::lock_guard<std::mutex> lk(g_side_mu);
+  VAFA_CUDA_CHECK(cudaStreamWaitEvent(s, ss->joined, 0));
+  return 0;
+}
+
+// Rejoins the side stream on every way out of a call (an error return included: a stream capture must
+// not end with the side stream still forked).
+struct SideGuard {
+  cudaStream_t s;
+  SideStream* ss = nullptr;
+  explicit SideGuard(cudaStream_t stream) : s(stream) {}
+  int join() {
+    SideStream* t = ss;
+    ss = nullptr;
+    return t ? side_join(s, t) : 0;
+  }
+  ~SideGuard() { join(); }
+};
+
 size_t absorb_fwd_ws_bytes(const vafa_absorb_args* a, bool inner) {
   const AbsorbFast f = absorb_fast(a, inner);
   size_t n = 0;
@@ -179,6 +240,20 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   const void* u;
   void* axn;
   int rc;
+  // the tile list is built on the side stream while the projection runs
+  SideGuard side(s);
+  AbsorbCoreArgs c{nullptr, a->x, nullptr, a->lse, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H, a->dtype,
+                   a->scale, a->sm_count, nullptr, a->status, x_width_of(a), 0};
+  if (fast.core) {
+    c.workspace = ws + ((!inner && fast.prologue) ? align_up((size_t)a->d_q * H * dkv * elem_size(a->dtype), 256) : 0);
+    if (!inner) {
+      if ((rc = side_fork(s, &side.ss))) return rc;
+      rc = sm100_absorb_core_fwd_lists(c, side.ss->stream);
+      const int rd = side_done(side.ss);
+      if (rc || rd) return rc ? rc : rd;
+      c.lists_built = 1;
+    }
+  }
   if (inner) {
     u = a->q_raw;
     axn = sv;
@@ -208,9 +283,10 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     if ((rc = simt_gemm(g2, s))) return rc;
     u = ub;
   }
+  if ((rc = side.join())) return rc;
   if (fast.core) {
-    AbsorbCoreArgs c{u, a->x, axn, a->lse, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H, a->dtype,
-                     a->scale, a->sm_count, ws, a->status, x_width_of(a)};
+    c.u = u;
+    c.axn = axn;
     if ((rc = sm100_absorb_core_fwd(c, s))) return rc;
   } else {
     SimtAttnParams p = simt_from_absorb(a, u, axn);
@@ -271,6 +347,19 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   // weight-gradient chain on the tensor-core GEMMs: needs the dU/dX fast path's preconditions, D_H = 32
   // (the 64-column box trick of the token reductions) and, for the full operator, d_q = 256
   const bool fast_chain = absorb_bwd_core_fast(a, inner) && dh == 32 && (inner || (dq >= 256 && dq % 256 == 0));
+  // tile lists of the dU and dX kernels: built on the side stream beside the products below
+  SideGuard side(s);
+  AbsorbCoreBwdArgs cb{u, a->x, dax, nullptr, du, a->dx, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H,
+                       a->dtype, a->scale, a->sm_count, nullptr, a->status, x_width_of(a), 0};
+  if (absorb_bwd_core_fast(a, inner)) {
+    const AbsorbBwdExtra x = absorb_bwd_extra(a);
+    cb.workspace = ws + z.dax + z.delta + z.du + z.dp + x.ld + x.bexp;
+    if ((rc = side_fork(s, &side.ss))) return rc;
+    rc = sm100_absorb_core_bwd_lists(cb, side.ss->stream);
+    const int rd = side_done(side.ss);
+    if (rc || rd) return rc ? rc : rd;
+    cb.lists_built = 1;
+  }
   if (!inner && absorb_fast(a, false).prologue) {
     // the tcgen05 prologue goes straight to u; the weight-gradient chain below needs p = q_raw W_Q
     if (fast_chain) {
@@ -288,13 +377,12 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     char* ex = ws + z.dax + z.delta + z.du + z.dp;
     void* ld = ex;
     void* bexp = ex + x.ld;
-    void* sched = ex + x.ld + x.bexp;
     if ((rc = sm100_absorb_expand_wv(a->w_v, bexp, H, dh, dkv, a->dtype, s))) return rc;
     GemmNNArgs gd{a->d_o, bexp, dax, Tq, H * dkv, H * dh, H * dkv, H * dkv, a->dtype, 0, a->sm_count};
     if ((rc = sm100_gemm_nn_k256(gd, s))) return rc;
     if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->dtype, s))) return rc;
-    AbsorbCoreBwdArgs cb{u, a->x, dax, ld, du, a->dx, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H,
-                         a->dtype, a->scale, a->sm_count, sched, a->status, x_width_of(a)};
+    cb.ld = ld;
+    if ((rc = side.join())) return rc;
     if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
   } else {
     // dax_h = dO_h W_V_h^T                  fp32 [T_q, H, d_kv]
