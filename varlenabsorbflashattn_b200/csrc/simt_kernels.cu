@@ -277,6 +277,48 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(SimtGemm g) {
   }
 }
 
+// W_QK tile: 32 rows of W_Q against all of W_K for one head.  The general kernel above gives a CTA one
+// 16 x 16 tile (8192 CTAs with 32 multiply-adds per thread for the production widths: 36 us for 0.13 GFLOP);
+// here a thread owns output columns kv = tid, tid + 256, ... of all 32 rows, with W_K's slice of the head
+// and the W_Q rows staged in shared memory 32 head-dim columns at a time.
+constexpr int kWqkRows = 32;
+template <typename T>
+__global__ void __launch_bounds__(256) absorb_wqk_kernel(const T* __restrict__ w_q, const T* __restrict__ w_k, T* __restrict__ out,
+                                                         int d_q, int d_kv, int H, int D_H) {
+  __shared__ float ks[256][33];
+  __shared__ float qs[kWqkRows][33];
+  const int h = blockIdx.y, a0 = blockIdx.x * kWqkRows, tid = threadIdx.x;
+  for (int kv0 = 0; kv0 < d_kv; kv0 += 256) {
+    float acc[kWqkRows];
+#pragma unroll
+    for (int i = 0; i < kWqkRows; ++i) acc[i] = 0.f;
+    for (int d0 = 0; d0 < D_H; d0 += 32) {
+      __syncthreads();
+      for (int i = tid; i < 256 * 32; i += 256) {
+        const int kv = kv0 + (i >> 5), dd = d0 + (i & 31);
+        ks[i >> 5][i & 31] = (kv < d_kv && dd < D_H) ? to_float(w_k[((long long)kv * H + h) * D_H + dd]) : 0.f;
+      }
+      for (int i = tid; i < kWqkRows * 32; i += 256) {
+        const int a = a0 + (i >> 5), dd = d0 + (i & 31);
+        qs[i >> 5][i & 31] = (a < d_q && dd < D_H) ? to_float(w_q[((long long)a * H + h) * D_H + dd]) : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int dd = 0; dd < 32; ++dd) {
+        const float kvv = ks[tid][dd];
+#pragma unroll
+        for (int i = 0; i < kWqkRows; ++i) acc[i] = fmaf(qs[i][dd], kvv, acc[i]);
+      }
+    }
+    const int kv = kv0 + tid;
+    if (kv < d_kv) {
+#pragma unroll
+      for (int i = 0; i < kWqkRows; ++i)
+        if (a0 + i < d_q) out[((long long)(a0 + i) * H + h) * d_kv + kv] = from_float<T>(acc[i]);
+    }
+  }
+}
+
 template <typename T>
 __global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -381,6 +423,21 @@ int simt_gemm(const SimtGemm& g, cudaStream_t s) {
   }
   if (rc) return rc;
   VAFA_LAUNCH_CHECK("simt_gemm_kernel");
+  return 0;
+}
+
+int absorb_wqk(const void* w_q, const void* w_k, void* w_qk, int d_q, int d_kv, int H, int D_H, int dtype, cudaStream_t s) {
+  if (d_q <= 0 || d_kv <= 0 || H <= 0) return 0;
+  if (H > 65535) return fail(VAFA_ERR_UNSUPPORTED, "absorb_wqk: %d heads", H);
+  const dim3 grid((d_q + kWqkRows - 1) / kWqkRows, H);
+  LaunchScope scope(kKSimtGemm, s);
+  if (dtype == VAFA_BF16)
+    absorb_wqk_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)w_q, (const __nv_bfloat16*)w_k, (__nv_bfloat16*)w_qk, d_q, d_kv, H, D_H);
+  else if (dtype == VAFA_F16)
+    absorb_wqk_kernel<__half><<<grid, 256, 0, s>>>((const __half*)w_q, (const __half*)w_k, (__half*)w_qk, d_q, d_kv, H, D_H);
+  else
+    return fail(VAFA_ERR_UNSUPPORTED, "absorb_wqk: 16-bit weights only");
+  VAFA_LAUNCH_CHECK("absorb_wqk_kernel");
   return 0;
 }
 

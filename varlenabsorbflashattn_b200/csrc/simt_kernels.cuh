@@ -45,4 +45,8 @@ int simt_gemm(const SimtGemm& g, cudaStream_t s);
 
 int cast_from_f32(const float* src, void* dst, size_t n, int dtype, cudaStream_t s);
 
+// W_QK[a, h, kv] = sum_dd W_Q[a, h, dd] * W_K[kv, h, dd]: the per-head product of the two absorbed
+// projections, [d_q, H, d_kv] in the weights' 16-bit dtype (fp32 accumulation).
+int absorb_wqk(const void* w_q, const void* w_k, void* w_qk, int d_q, int d_kv, int H, int D_H, int dtype, cudaStream_t s);
+
 }  // namespace vafa

@@ -564,48 +564,68 @@ __global__ void __launch_bounds__(sched_impl::kSchedThreads) bwd_prepare_kernel(
     sched_impl::sched_build(blockIdx.x == 0 ? sched_dq : sched_dkv);
     return;
   }
-  // D/8 lanes per (token, head) row, 16 bytes each; a warp takes 32/(D/8) rows per step and four steps,
-  // with all eight loads of a thread in flight before the first is used
-  constexpr int kLanes = D / 8, kRowsPerStep = 32 / kLanes, kSteps = 4;
+  // D/8 lanes per (token, head) row, 16 bytes each; a warp takes 32/(D/8) rows per step and kSteps steps
+  // per group.  The data CTAs stay resident (one per SM) and stride over the groups with the next group's
+  // loads in flight while the current one is reduced and written: with one short-lived CTA per 256 rows
+  // the loads, the arithmetic and the stores of an SM ran one after the other, wave by wave.
+  constexpr int kLanes = D / 8, kRowsPerStep = 32 / kLanes, kSteps = 2;
   const int lane = threadIdx.x & 31, sub = lane / kLanes, li = lane % kLanes;
   const long long n_rows = (long long)total_q * H;
   constexpr int kWarpsPerCta = sched_impl::kSchedThreads / 32;
-  const long long row0 = ((long long)(blockIdx.x - 2) * kWarpsPerCta + (threadIdx.x >> 5)) * (kRowsPerStep * kSteps) + sub;
-  uint4 a[kSteps], b[kSteps];
+  constexpr int kRowsPerGroup = kRowsPerStep * kSteps;
+  const long long n_groups = (n_rows + kRowsPerGroup - 1) / kRowsPerGroup;
+  const long long n_warps = (long long)(gridDim.x - 2) * kWarpsPerCta;
+  auto load = [&](long long grp, uint4 (&a)[kSteps], uint4 (&b)[kSteps]) {
 #pragma unroll
-  for (int st = 0; st < kSteps; ++st) {
-    const long long row = row0 + st * kRowsPerStep;
-    a[st] = b[st] = make_uint4(0u, 0u, 0u, 0u);
-    if (row < n_rows) {
-      a[st] = reinterpret_cast<const uint4*>(o + row * D)[li];
-      b[st] = reinterpret_cast<const uint4*>(d_o + row * D)[li];
-    }
-  }
-#pragma unroll
-  for (int st = 0; st < kSteps; ++st) {
-    const long long row = row0 + st * kRowsPerStep;
-    const T* pa = reinterpret_cast<const T*>(&a[st]);
-    const T* pb = reinterpret_cast<const T*>(&b[st]);
-    float part = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) part += to_float(pa[i]) * to_float(pb[i]);
-#pragma unroll
-    for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-    if (row < n_rows && li < 4) {
-      const int t = (int)(row / H), h = (int)(row % H);
-      const float l = lse[row];
-      if (li == 0) ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
-      // fold row: 32 elements = 64 B = four 16-byte pieces, one per lane
-      uint4 v = make_uint4(0u, 0u, 0u, 0u);
-      if (li == 0) {
-        const uint2 fl = fold_pieces<T>(l == -INFINITY ? -INFINITY : -l * inv_c);
-        v.x = fl.x; v.y = fl.y;
-      } else if (li == 2) {
-        const uint2 fd = fold_pieces<T>(-part);
-        v.x = fd.x; v.y = fd.y;
+    for (int st = 0; st < kSteps; ++st) {
+      const long long row = grp * kRowsPerGroup + st * kRowsPerStep + sub;
+      a[st] = b[st] = make_uint4(0u, 0u, 0u, 0u);
+      if (row < n_rows) {
+        a[st] = reinterpret_cast<const uint4*>(o + row * D)[li];
+        b[st] = reinterpret_cast<const uint4*>(d_o + row * D)[li];
       }
-      fold[row * 4 + li] = v;
     }
+  };
+  auto reduce_and_store = [&](long long grp, const uint4 (&a)[kSteps], const uint4 (&b)[kSteps]) {
+#pragma unroll
+    for (int st = 0; st < kSteps; ++st) {
+      const long long row = grp * kRowsPerGroup + st * kRowsPerStep + sub;
+      const T* pa = reinterpret_cast<const T*>(&a[st]);
+      const T* pb = reinterpret_cast<const T*>(&b[st]);
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+#pragma unroll
+      for (int off = kLanes / 2; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+      if (row < n_rows && li < 4) {
+        const int t = (int)(row / H), h = (int)(row % H);
+        const float l = lse[row];
+        if (li == 0) ld[(long long)h * ld_stride + t] = make_float2(l == -INFINITY ? INFINITY : l, part);
+        // fold row: 32 elements = 64 B = four 16-byte pieces, one per lane
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (li == 0) {
+          const uint2 fl = fold_pieces<T>(l == -INFINITY ? -INFINITY : -l * inv_c);
+          v.x = fl.x; v.y = fl.y;
+        } else if (li == 2) {
+          const uint2 fd = fold_pieces<T>(-part);
+          v.x = fd.x; v.y = fd.y;
+        }
+        fold[row * 4 + li] = v;
+      }
+    }
+  };
+  uint4 a0[kSteps], b0[kSteps], a1[kSteps], b1[kSteps];
+  long long grp = (long long)(blockIdx.x - 2) * kWarpsPerCta + (threadIdx.x >> 5);
+  if (grp < n_groups) load(grp, a0, b0);
+  // two groups per trip so that the register sets swap roles without copies
+  while (grp < n_groups) {
+    const long long g1 = grp + n_warps, g2 = g1 + n_warps;
+    if (g1 < n_groups) load(g1, a1, b1);
+    reduce_and_store(grp, a0, b0);
+    if (g1 >= n_groups) break;
+    if (g2 < n_groups) load(g2, a0, b0);
+    reduce_and_store(g1, a1, b1);
+    grp = g2;
   }
 }
 
@@ -660,8 +680,11 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   float2* ld = (float2*)(base + ws.ld);
   {
     const long long n = (long long)a->total_q * a->num_heads;
-    constexpr int kRowsPerCta = (32 / (D / 8)) * 4 * (sched_impl::kSchedThreads / 32);
-    const unsigned grid = 2u + (unsigned)((n + kRowsPerCta - 1) / kRowsPerCta);
+    // two list-building CTAs plus resident data CTAs: one per remaining SM, fewer for small batches
+    constexpr int kRowsPerCtaTrip = (32 / (D / 8)) * 2 * (sched_impl::kSchedThreads / 32);
+    const long long want = (n + kRowsPerCtaTrip - 1) / kRowsPerCtaTrip;
+    const long long room = sms > 3 ? sms - 2 : 1;
+    const unsigned grid = 2u + (unsigned)(want < room ? (want > 0 ? want : 1) : room);
     LaunchScope scope(kKBwdPre, s);
     bwd_prepare_kernel<T, D><<<grid, sched_impl::kSchedThreads, 0, s>>>(
         sq, sk, (const T*)a->o, (const T*)a->d_o, a->lse, ld, (uint4*)(base + ws.fold), 1.f / (a->scale * kLog2e),
@@ -696,6 +719,31 @@ __global__ void __launch_bounds__(256) absorb_ld_kernel(const T* __restrict__ o,
   for (int d = 0; d < D_H; ++d) acc += to_float(a[d]) * to_float(b[d]);
   const float l = lse[i];
   ld[i] = make_float2(l == -INFINITY ? INFINITY : l, acc);
+}
+
+// The same with D_H/8 lanes per row and 16-byte loads (D_H = 8, 16, ..., 256): a warp reads whole lines.
+template <typename T>
+__global__ void __launch_bounds__(256) absorb_ld_vec_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
+                                                            const float* __restrict__ lse, float2* __restrict__ ld,
+                                                            long long n_rows, int lanes_log2) {
+  const int lanes = 1 << lanes_log2;  // lanes per row, <= 32
+  const long long gi = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long row = gi >> lanes_log2;
+  const int li = (int)(gi & (lanes - 1));
+  float part = 0.f;
+  if (row < n_rows) {
+    const uint4 a = reinterpret_cast<const uint4*>(o + (row << (lanes_log2 + 3)))[li];
+    const uint4 b = reinterpret_cast<const uint4*>(d_o + (row << (lanes_log2 + 3)))[li];
+    const T* pa = reinterpret_cast<const T*>(&a);
+    const T* pb = reinterpret_cast<const T*>(&b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part += to_float(pa[i]) * to_float(pb[i]);
+  }
+  for (int off = lanes >> 1; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+  if (row < n_rows && li == 0) {
+    const float l = lse[row];
+    ld[row] = make_float2(l == -INFINITY ? INFINITY : l, part);
+  }
 }
 
 // Bexp[(h',dd), (h,kv)] = W_V[kv,h,dd] if h == h' else 0: with it dAlphaX = dO . Bexp is one dense
@@ -824,6 +872,18 @@ int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
 int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s) {
   if (n_rows <= 0) return 0;
   LaunchScope scope(kKBwdPre, s);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o)) & 15) == 0;
+  if (aligned && D_H >= 8 && D_H <= 256 && (D_H & (D_H - 1)) == 0) {
+    int lanes_log2 = 0;
+    while ((8 << lanes_log2) < D_H) ++lanes_log2;
+    const unsigned vgrid = (unsigned)(((n_rows << lanes_log2) + 255) / 256);
+    if (dtype == VAFA_BF16)
+      absorb_ld_vec_kernel<__nv_bfloat16><<<vgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, lanes_log2);
+    else
+      absorb_ld_vec_kernel<__half><<<vgrid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, lanes_log2);
+    VAFA_LAUNCH_CHECK("absorb_ld_vec_kernel");
+    return 0;
+  }
   const unsigned grid = (unsigned)((n_rows + 255) / 256);
   if (dtype == VAFA_BF16)
     absorb_ld_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, D_H);

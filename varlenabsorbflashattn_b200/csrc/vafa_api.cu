@@ -261,9 +261,7 @@ int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     // W_QK[a, h, kv] = sum_dd W_Q[a,h,dd] W_K[kv,h,dd]  (tiny), then u = q_raw . W_QK as one product
     void* wqk = ws;
     ws += align_up((size_t)a->d_q * H * dkv * elem_size(a->dtype), 256);
-    SimtGemm gw{a->w_q, a->w_k, wqk, a->dtype, a->dtype, a->dtype, a->d_q, dkv, dh, H,
-                (int64_t)H * dh, 1, dh, 1, (int64_t)H * dh, dh, (int64_t)H * dkv, 1, dkv, 1.f};
-    if ((rc = simt_gemm(gw, s))) return rc;
+    if ((rc = absorb_wqk(a->w_q, a->w_k, wqk, a->d_q, dkv, H, dh, a->dtype, s))) return rc;
     void* ub = sv + z.p;
     axn = sv + z.p + z.u;
     GemmNNArgs g{a->q_raw, wqk, ub, Tq, H * dkv, a->d_q, H * dkv, H * dkv, a->dtype, 0, a->sm_count};
