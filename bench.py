@@ -238,6 +238,29 @@ def absorb_leg(dev, steps, warmup, group, production=False):
         ms = e0.elapsed_time(e1) / steps
         out[name + "_ms"] = ms
         out[name + "_keys_per_s"] = Tk / (ms * 1e-3)
+    # The same forward+backward replayed from a CUDA graph: a step of this size is some 25 short launches,
+    # so the eager number above contains the host's launch rate; the replay is the device time.
+    if group is None:
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fb()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fb()
+        for _ in range(warmup):
+            graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out["fwd_bwd_graph_ms"] = ms
+        out["fwd_bwd_graph_keys_per_s"] = Tk / (ms * 1e-3)
     out["workload"] = ("production-like: 1137 users, 97 % with 2048 keys, q 1-18 (mean 5.3), d_q=968, d_kv=216, "
                        f"H=8, D_H=32, bf16 ({Tq} queries, {Tk} keys)" if production else
                        "C4: 1024 users, q U[1,16], k logU[8,2048], d=256, H=8, D_H=32, bf16")

@@ -281,33 +281,60 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(SimtGemm g) {
 // 16 x 16 tile (8192 CTAs with 32 multiply-adds per thread for the production widths: 36 us for 0.13 GFLOP);
 // here a thread owns output columns kv = tid, tid + 256, ... of all 32 rows, with W_K's slice of the head
 // and the W_Q rows staged in shared memory 32 head-dim columns at a time.
-constexpr int kWqkRows = 32;
+constexpr int kWqkRows = 16;
 template <typename T>
 __global__ void __launch_bounds__(256) absorb_wqk_kernel(const T* __restrict__ w_q, const T* __restrict__ w_k, T* __restrict__ out,
                                                          int d_q, int d_kv, int H, int D_H) {
-  __shared__ float ks[256][33];
-  __shared__ float qs[kWqkRows][33];
+  __shared__ float ks[256][33];                          // [kv][dd]
+  __shared__ __align__(16) float qs[32][kWqkRows];       // [dd][row]: a float4 serves four rows
   const int h = blockIdx.y, a0 = blockIdx.x * kWqkRows, tid = threadIdx.x;
+  const bool vec = (D_H % 8) == 0;  // 16-byte loads (the launcher checks the bases)
   for (int kv0 = 0; kv0 < d_kv; kv0 += 256) {
     float acc[kWqkRows];
 #pragma unroll
     for (int i = 0; i < kWqkRows; ++i) acc[i] = 0.f;
     for (int d0 = 0; d0 < D_H; d0 += 32) {
       __syncthreads();
-      for (int i = tid; i < 256 * 32; i += 256) {
-        const int kv = kv0 + (i >> 5), dd = d0 + (i & 31);
-        ks[i >> 5][i & 31] = (kv < d_kv && dd < D_H) ? to_float(w_k[((long long)kv * H + h) * D_H + dd]) : 0.f;
-      }
-      for (int i = tid; i < kWqkRows * 32; i += 256) {
-        const int a = a0 + (i >> 5), dd = d0 + (i & 31);
-        qs[i >> 5][i & 31] = (a < d_q && dd < D_H) ? to_float(w_q[((long long)a * H + h) * D_H + dd]) : 0.f;
+      if (vec) {
+        for (int i = tid; i < 256 * 4; i += 256) {
+          const int kv = kv0 + (i >> 2), dd = d0 + (i & 3) * 8;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (kv < d_kv && dd < D_H) v = *reinterpret_cast<const uint4*>(w_k + ((long long)kv * H + h) * D_H + dd);
+          const T* pv = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) ks[i >> 2][(i & 3) * 8 + e] = to_float(pv[e]);
+        }
+        if (tid < kWqkRows * 4) {
+          const int a = a0 + (tid >> 2), dd = d0 + (tid & 3) * 8;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (a < d_q && dd < D_H) v = *reinterpret_cast<const uint4*>(w_q + ((long long)a * H + h) * D_H + dd);
+          const T* pv = reinterpret_cast<const T*>(&v);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) qs[(tid & 3) * 8 + e][tid >> 2] = to_float(pv[e]);
+        }
+      } else {
+        for (int i = tid; i < 256 * 32; i += 256) {
+          const int kv = kv0 + (i >> 5), dd = d0 + (i & 31);
+          ks[i >> 5][i & 31] = (kv < d_kv && dd < D_H) ? to_float(w_k[((long long)kv * H + h) * D_H + dd]) : 0.f;
+        }
+        for (int i = tid; i < kWqkRows * 32; i += 256) {
+          const int a = a0 + (i >> 5), dd = d0 + (i & 31);
+          qs[i & 31][i >> 5] = (a < d_q && dd < D_H) ? to_float(w_q[((long long)a * H + h) * D_H + dd]) : 0.f;
+        }
       }
       __syncthreads();
 #pragma unroll 8
       for (int dd = 0; dd < 32; ++dd) {
         const float kvv = ks[tid][dd];
+        const float4* q4 = reinterpret_cast<const float4*>(qs[dd]);
 #pragma unroll
-        for (int i = 0; i < kWqkRows; ++i) acc[i] = fmaf(qs[i][dd], kvv, acc[i]);
+        for (int i = 0; i < kWqkRows / 4; ++i) {
+          const float4 q = q4[i];
+          acc[4 * i + 0] = fmaf(q.x, kvv, acc[4 * i + 0]);
+          acc[4 * i + 1] = fmaf(q.y, kvv, acc[4 * i + 1]);
+          acc[4 * i + 2] = fmaf(q.z, kvv, acc[4 * i + 2]);
+          acc[4 * i + 3] = fmaf(q.w, kvv, acc[4 * i + 3]);
+        }
       }
     }
     const int kv = kv0 + tid;
@@ -429,6 +456,8 @@ int simt_gemm(const SimtGemm& g, cudaStream_t s) {
 int absorb_wqk(const void* w_q, const void* w_k, void* w_qk, int d_q, int d_kv, int H, int D_H, int dtype, cudaStream_t s) {
   if (d_q <= 0 || d_kv <= 0 || H <= 0) return 0;
   if (H > 65535) return fail(VAFA_ERR_UNSUPPORTED, "absorb_wqk: %d heads", H);
+  if (((reinterpret_cast<uintptr_t>(w_q) | reinterpret_cast<uintptr_t>(w_k)) & 15) != 0)
+    return fail(VAFA_ERR_INVALID, "absorb_wqk: weights must be 16-byte aligned");
   const dim3 grid((d_q + kWqkRows - 1) / kWqkRows, H);
   LaunchScope scope(kKSimtGemm, s);
   if (dtype == VAFA_BF16)
