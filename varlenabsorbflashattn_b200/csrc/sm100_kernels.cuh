@@ -70,7 +70,12 @@ int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);
 // orders before the core call), so that the single-CTA list builder runs beside the projections.
 int sm100_absorb_core_fwd_lists(const AbsorbCoreArgs& a, cudaStream_t s);
 int sm100_absorb_core_bwd_lists(const AbsorbCoreBwdArgs& a, cudaStream_t s);
-int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s);
+// (lse, delta) rows of the absorb backward: a float2 array of n_pad entries followed by two planar float
+// arrays of n_pad entries each (-lse and -delta * scale, for the dX kernel); n_pad = sm100_absorb_ld_pad().
+inline long long sm100_absorb_ld_pad(long long n_rows) { return (n_rows + 128 + 3) & ~3LL; }
+size_t sm100_absorb_ld_bytes(long long n_rows);
+int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, float scale, int dtype,
+                    cudaStream_t s);
 int sm100_absorb_expand_wv(const void* w_v, void* bexp, int H, int D_H, int d_kv, int dtype, cudaStream_t s);
 
 // C[M, ldc] (16-bit) = A[M, K] . B[K, N] with A rows densely packed (K = lda, a multiple of 256) and B

@@ -46,6 +46,7 @@ using namespace ptx;
 constexpr int kBwdThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
 constexpr int kLdRow = 68;        // float2 slots per staged (lse, delta) block: 64 + 2 of alignment slack, padded
 constexpr int kInner = 64;  // rows per inner block
+constexpr int kPlanarRow = 72;  // floats per staged planar block: 64 + 3 of alignment slack, padded; 68 are copied
 
 template <int D>
 struct BwdCfg {
@@ -77,7 +78,11 @@ struct BwdSmem {
   alignas(8) uint64_t outer_full, outer_free;
   uint64_t in_full[kS], in_empty[kS];
   uint64_t xy_full[2], ds_full[2], acc_done;
-  alignas(16) float2 ld[kS][kDKV ? kLdRow : 2];  // dKV: (lse, delta) of the inner block's query rows
+  alignas(16) float2 ld[kS][(kDKV && !kAbsorb) ? kLdRow : 2];  // dKV: (lse, delta) of the inner block's query rows
+  // absorb dX: the same two numbers planar, as -lse and -delta * scale, so that a pair of neighbouring
+  // columns is one 8-byte operand of the packed fp32 instructions
+  alignas(16) float nl[kS][(kDKV && kAbsorb) ? kPlanarRow : 4];
+  alignas(16) float nd[kS][(kDKV && kAbsorb) ? kPlanarRow : 4];
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
@@ -202,8 +207,17 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           if (kOneInner && b + kPrefetch < nb)
             for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_inner_a, c * 64, h, row + kPrefetch * ib);
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.in_empty[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
-          mbar_expect_tx(smem_u32(&sm.in_full[st]), (kOneInner ? 1 : 2) * Cfg::kInnerBytes + (kDKV ? 66 * 8 : 0));
-          if (kDKV) {
+          mbar_expect_tx(smem_u32(&sm.in_full[st]),
+                         (kOneInner ? 1 : 2) * Cfg::kInnerBytes + (kDKV ? (kAbsorb ? 2 * 68 * 4 : 66 * 8) : 0));
+          if (kDKV && kAbsorb) {
+            // planar -lse and -delta*scale of the block's 64 stacked rows, from the 16-byte boundary at or
+            // below the first (readers skip first & 3 slots); the arrays follow the float2 array
+            const long long first = (long long)row * p.H;
+            const float* nlg = reinterpret_cast<const float*>(p.ld + p.ld_stride);
+            const float* ndg = nlg + p.ld_stride;
+            bulk_load_1d(smem_u32(&sm.nl[st][0]), nlg + (first & ~3LL), 68 * 4, smem_u32(&sm.in_full[st]));
+            bulk_load_1d(smem_u32(&sm.nd[st][0]), ndg + (first & ~3LL), 68 * 4, smem_u32(&sm.in_full[st]));
+          } else if (kDKV) {
             // (lse, delta) pairs of the block's 64 inner columns: the copy starts at the even index
             // at or below the first pair (16-byte alignment) and takes 66 pairs; readers skip
             // (index & 1) slots
@@ -450,7 +464,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             for (int e = 0; e < 2; ++e) {
               const int col = half * 32 + i + e;
               float lse_v, delta_v;
-              if (kDKV) {
+              if (kDKV && !kAbsorb) {
                 const float2 t = sm.ld[st][ld_skip + col];
                 lse_v = t.x;
                 delta_v = t.y;
@@ -481,7 +495,57 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
             tmem_st16(y_addr + half * 32, dd);
           }
         };
-        if (__any_sync(0xffffffffu, need_mask)) block_body(std::true_type{}); else block_body(std::false_type{});
+        if constexpr (kDKV && kAbsorb) {
+          // absorb dX: the staged -lse / -delta*scale rows of columns past the user's last stacked row (they
+          // belong to the next user, or to the padding) become -inf / 0, which makes P and dS exact zeros
+          // there without a compare per element; then packed fp32 pairs all the way:
+          //   P = 2^(S c - lse),  dS = P (dP scale - delta scale)
+          const int skip = (int)(((long long)(w.i_start + b * ib) * p.H) & 3);
+          if (hi < kInner - 1) {  // same for every thread: the absorb operator has no causal mask
+            const int t = threadIdx.x;
+            if (t < kInner && t > hi) {
+              sm.nl[st][skip + t] = -INFINITY;
+              sm.nd[st][skip + t] = 0.f;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+          }
+          uint32_t xs[32], ys[32];
+          tmem_ld32(x_addr + half * 32, xs);
+          tmem_ld32(y_addr + half * 32, ys);
+          tmem_wait_ld();
+          uint32_t pp[16], dd[16];
+          const uint64_t c2 = pack_f2(c, c), s2 = pack_f2(p.scale, p.scale);
+          const float* nlp = &sm.nl[st][skip + half * 32];
+          const float* ndp = &sm.nd[st][skip + half * 32];
+          auto pairs = [&](auto even_tag) {
+            constexpr bool kEven = decltype(even_tag)::value;  // 8-byte aligned pairs
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float2 n2, d2;
+              if (kEven) {
+                n2 = *reinterpret_cast<const float2*>(nlp + 2 * i);
+                d2 = *reinterpret_cast<const float2*>(ndp + 2 * i);
+              } else {
+                n2 = make_float2(nlp[2 * i], nlp[2 * i + 1]);
+                d2 = make_float2(ndp[2 * i], ndp[2 * i + 1]);
+              }
+              const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(xs[2 * i]), __uint_as_float(xs[2 * i + 1])), c2, pack_f2(n2.x, n2.y));
+              float t0, t1;
+              unpack_f2(t2, t0, t1);
+              const float p0 = ex2(t0), p1 = ex2(t1);
+              const uint64_t u2 = fma_f2(pack_f2(__uint_as_float(ys[2 * i]), __uint_as_float(ys[2 * i + 1])), s2, pack_f2(d2.x, d2.y));
+              float e0, e1;
+              unpack_f2(mul_f2(pack_f2(p0, p1), u2), e0, e1);
+              pp[i] = pack2<T>(p0, p1);
+              dd[i] = pack2<T>(e0, e1);
+            }
+          };
+          if ((skip & 1) == 0) pairs(std::true_type{}); else pairs(std::false_type{});
+          tmem_st16(x_addr + half * 32, pp);
+          tmem_st16(y_addr + half * 32, dd);
+        } else {
+          if (__any_sync(0xffffffffu, need_mask)) block_body(std::true_type{}); else block_body(std::false_type{});
+        }
         tmem_wait_st();
         // The previous item's accumulator is read back here, after this item's first block has been
         // through the element-wise phase and before its products are released (they overwrite the
@@ -706,26 +770,37 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
 
 
 // ---------------- absorb operator: backward core ---------------------------------------------
-// LD[t*H + h] = (lse, or +inf where the row saw no key; delta = sum_d O*dO), token-major.
+// LD[t*H + h] = (lse, or +inf where the row saw no key; delta = sum_d O*dO), token-major, followed by
+// the same numbers planar for the dX kernel: NL[row] = -LD.x and ND[row] = -delta * scale, each n_pad
+// long (n_pad = n_rows + padding, a multiple of 4; the padding rows hold -inf / 0).
 template <typename T>
 __global__ void __launch_bounds__(256) absorb_ld_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                         const float* __restrict__ lse, float2* __restrict__ ld,
-                                                        long long n_rows, int D_H) {
+                                                        long long n_rows, long long n_pad, float scale, int D_H) {
   const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-  if (i >= n_rows) return;
+  if (i >= n_pad) return;
+  float* nl = reinterpret_cast<float*>(ld + n_pad);
+  float* nd = nl + n_pad;
+  if (i >= n_rows) {
+    nl[i] = -INFINITY;
+    nd[i] = 0.f;
+    return;
+  }
   const T* a = o + i * D_H;
   const T* b = d_o + i * D_H;
   float acc = 0.f;
   for (int d = 0; d < D_H; ++d) acc += to_float(a[d]) * to_float(b[d]);
   const float l = lse[i];
   ld[i] = make_float2(l == -INFINITY ? INFINITY : l, acc);
+  nl[i] = (l == -INFINITY) ? -INFINITY : -l;
+  nd[i] = -acc * scale;
 }
 
 // The same with D_H/8 lanes per row and 16-byte loads (D_H = 8, 16, ..., 256): a warp reads whole lines.
 template <typename T>
 __global__ void __launch_bounds__(256) absorb_ld_vec_kernel(const T* __restrict__ o, const T* __restrict__ d_o,
                                                             const float* __restrict__ lse, float2* __restrict__ ld,
-                                                            long long n_rows, int lanes_log2) {
+                                                            long long n_rows, long long n_pad, float scale, int lanes_log2) {
   const int lanes = 1 << lanes_log2;  // lanes per row, <= 32
   const long long gi = (long long)blockIdx.x * 256 + threadIdx.x;
   const long long row = gi >> lanes_log2;
@@ -740,9 +815,18 @@ __global__ void __launch_bounds__(256) absorb_ld_vec_kernel(const T* __restrict_
     for (int i = 0; i < 8; ++i) part += to_float(pa[i]) * to_float(pb[i]);
   }
   for (int off = lanes >> 1; off > 0; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
-  if (row < n_rows && li == 0) {
-    const float l = lse[row];
-    ld[row] = make_float2(l == -INFINITY ? INFINITY : l, part);
+  if (li == 0 && row < n_pad) {
+    float* nl = reinterpret_cast<float*>(ld + n_pad);
+    float* nd = nl + n_pad;
+    if (row < n_rows) {
+      const float l = lse[row];
+      ld[row] = make_float2(l == -INFINITY ? INFINITY : l, part);
+      nl[row] = (l == -INFINITY) ? -INFINITY : -l;
+      nd[row] = -part * scale;
+    } else {
+      nl[row] = -INFINITY;
+      nd[row] = 0.f;
+    }
   }
 }
 
@@ -822,7 +906,7 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   if ((rc = encode_tmap_rows(&g64, a.dax, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
 
   BwdParams p;
-  p.ld = (const float2*)a.ld; p.ld_stride = 0; p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
+  p.ld = (const float2*)a.ld; p.ld_stride = sm100_absorb_ld_pad((long long)a.total_q * a.H); p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
   p.out_width = a.x_width;
   p.trace = nullptr;
 #ifdef VAFA_TRACE
@@ -869,26 +953,30 @@ int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   return a.dtype == VAFA_BF16 ? launch_absorb_core_bwd<__nv_bfloat16>(a, s) : launch_absorb_core_bwd<__half>(a, s);
 }
 
-int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, int dtype, cudaStream_t s) {
+size_t sm100_absorb_ld_bytes(long long n_rows) { return (size_t)sm100_absorb_ld_pad(n_rows) * 16; }
+
+int sm100_absorb_ld(const void* o, const void* d_o, const float* lse, void* ld, long long n_rows, int D_H, float scale, int dtype,
+                    cudaStream_t s) {
   if (n_rows <= 0) return 0;
+  const long long n_pad = sm100_absorb_ld_pad(n_rows);
   LaunchScope scope(kKBwdPre, s);
   const bool aligned = ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(d_o)) & 15) == 0;
   if (aligned && D_H >= 8 && D_H <= 256 && (D_H & (D_H - 1)) == 0) {
     int lanes_log2 = 0;
     while ((8 << lanes_log2) < D_H) ++lanes_log2;
-    const unsigned vgrid = (unsigned)(((n_rows << lanes_log2) + 255) / 256);
+    const unsigned vgrid = (unsigned)(((n_pad << lanes_log2) + 255) / 256);
     if (dtype == VAFA_BF16)
-      absorb_ld_vec_kernel<__nv_bfloat16><<<vgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, lanes_log2);
+      absorb_ld_vec_kernel<__nv_bfloat16><<<vgrid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, n_pad, scale, lanes_log2);
     else
-      absorb_ld_vec_kernel<__half><<<vgrid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, lanes_log2);
+      absorb_ld_vec_kernel<__half><<<vgrid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, n_pad, scale, lanes_log2);
     VAFA_LAUNCH_CHECK("absorb_ld_vec_kernel");
     return 0;
   }
-  const unsigned grid = (unsigned)((n_rows + 255) / 256);
+  const unsigned grid = (unsigned)((n_pad + 255) / 256);
   if (dtype == VAFA_BF16)
-    absorb_ld_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, D_H);
+    absorb_ld_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, lse, (float2*)ld, n_rows, n_pad, scale, D_H);
   else
-    absorb_ld_kernel<__half><<<grid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, D_H);
+    absorb_ld_kernel<__half><<<grid, 256, 0, s>>>((const __half*)o, (const __half*)d_o, lse, (float2*)ld, n_rows, n_pad, scale, D_H);
   VAFA_LAUNCH_CHECK("absorb_ld_kernel");
   return 0;
 }

@@ -309,7 +309,7 @@ struct AbsorbBwdExtra {
 AbsorbBwdExtra absorb_bwd_extra(const vafa_absorb_args* a) {
   AbsorbBwdExtra x;
   const size_t H = a->num_heads;
-  x.ld = align_up(((size_t)a->total_q * H + 128) * 8, 256);
+  x.ld = align_up(sm100_absorb_ld_bytes((long long)a->total_q * H), 256);
   x.bexp = align_up(H * a->head_dim * H * a->d_kv * elem_size(a->dtype), 256);
   x.sched = sm100_absorb_core_bwd_workspace_bytes(a->total_q, a->total_k, a->n_seg, a->num_heads);
   const size_t t1 = sm100_gemm_tn_workspace_bytes(a->total_q, a->num_heads, 32, a->sm_count);
@@ -378,7 +378,7 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     if ((rc = sm100_absorb_expand_wv(a->w_v, bexp, H, dh, dkv, a->dtype, s))) return rc;
     GemmNNArgs gd{a->d_o, bexp, dax, Tq, H * dkv, H * dh, H * dkv, H * dkv, a->dtype, 0, a->sm_count};
     if ((rc = sm100_gemm_nn_k256(gd, s))) return rc;
-    if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->dtype, s))) return rc;
+    if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->scale, a->dtype, s))) return rc;
     cb.ld = ld;
     if ((rc = side.join())) return rc;
     if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
