@@ -15,8 +15,9 @@ ranks divided by the slowest rank's time.
 The JSON line also carries: `e2e` (same metric, host pinned buffers in, host buffers out, copies
 inside the timed region), `roofline` of the dominant kernel (event-timed inside this run),
 `cpu_baseline` (the fp32 torch CPU restatement of the reference's own oracle, timed on a bounded
-sample on this box's host cores), `absorb` (target-attention keys/s on configuration 4) and the
-GPU clocks sampled during the timed regions.
+sample on this box's host cores), `absorb` (target-attention keys/s on configuration 4 and on the
+production-like shape: forward, forward+backward, and the forward+backward step replayed from a CUDA
+graph, which leaves the host's launch rate out) and the GPU clocks sampled during the timed regions.
 """
 from __future__ import annotations
 
