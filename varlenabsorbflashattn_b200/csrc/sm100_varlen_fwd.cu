@@ -57,15 +57,23 @@ struct FwdCfg {
   static constexpr uint32_t kOCol = 256;
 };
 
+// Keys per block and ring depth of the key tiles.  The absorb operator's X tile serves both products of
+// its block, so its slot is held from the load to the end of P.X; with 128-key blocks (64 KB) only two
+// slots fit beside the 64 KB query tile and a load could start only when the block two back had finished.
+// Blocks of 96 keys (48 KB) leave room for three slots.
+template <bool kAbsorb> constexpr int fwd_block_keys() { return kAbsorb ? 96 : kTile; }
+template <bool kAbsorb> constexpr int fwd_key_stages() { return kAbsorb ? 3 : 2; }
+
 // kAbsorb: keys and values are the same rows (the absorb operator attends over raw X), so there
 // is one ring and no V tiles.
 template <int D, bool kAbsorb = false>
 struct FwdSmem {
   alignas(1024) uint8_t q[FwdCfg<D>::kTileBytes];
-  alignas(1024) uint8_t k[FwdCfg<D>::kStages][FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t k[fwd_key_stages<kAbsorb>()][FwdCfg<D>::kSub * fwd_block_keys<kAbsorb>() * 128];
   alignas(1024) uint8_t v[kAbsorb ? 1 : FwdCfg<D>::kStages][kAbsorb ? 1024 : FwdCfg<D>::kTileBytes];
   alignas(8) uint64_t q_full, q_free;
-  uint64_t k_full[2], v_full[2];
+  uint64_t k_full[3], v_full[2];
+  uint64_t k_empty[3];  // absorb: slot free again (P.X of its block complete)
   uint64_t s_full[2], p_full[2], o_done[2];  // indexed by block parity; phase = (block / 2) & 1
   uint64_t pair_bar[4];       // the two softmax warps of one TMEM lane quadrant
   float xmax[2][2][128];      // [block parity][half][row] partial row maxima
@@ -101,7 +109,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                   const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
   using Cfg = FwdCfg<D>;
-  constexpr int S = Cfg::kStages;
+  constexpr int S = fwd_key_stages<kAbsorb>();
+  constexpr int kBlk = fwd_block_keys<kAbsorb>();   // keys per block
+  constexpr int kHalf = kBlk / 2;                   // score columns per softmax thread
+  constexpr int kKSubBytes = kBlk * 128;            // one 64-column sub tile of a key tile
+  constexpr int kKTileBytes = Cfg::kSub * kKSubBytes;
   extern __shared__ uint8_t smem_raw[];
   using Smem = FwdSmem<D, kAbsorb>;
   Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,8 +128,9 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(smem_u32(&sm.q_free), 1);
     for (int i = 0; i < S; ++i) {
       mbar_init(smem_u32(&sm.k_full[i]), 1);
-      mbar_init(smem_u32(&sm.v_full[i]), 1);
+      mbar_init(smem_u32(&sm.k_empty[i]), 1);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&sm.v_full[i]), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.s_full[i]), 1);
       mbar_init(smem_u32(&sm.p_full[i]), 8);  // lane 0 of each softmax warp
@@ -159,7 +172,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (idx < 0) break;
         const WorkItem w = p.items[idx];
         const int h = w.head;
-        const int nb = (w.i_len + kTile - 1) / kTile;
+        const int nb = (w.i_len + kBlk - 1) / kBlk;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
         mbar_expect_tx(smem_u32(&sm.q_full), Cfg::kTileBytes);
@@ -172,18 +185,18 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         constexpr int kPrefetch = 4;
         if (kAbsorb)
           for (int b = 2; b < kPrefetch && b < nb; ++b)
-            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, w.i_start + b * kTile);
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, w.i_start + b * kBlk);
         for (int b = 0; b < nb; ++b, ++gk) {
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
-          const int row = w.i_start + b * kTile;
+          const int row = w.i_start + b * kBlk;
           if (kAbsorb && b + kPrefetch < nb)
-            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, row + kPrefetch * kTile);
-          // slot free: S(gk-2) complete (absorb: P.X(gk-2) complete, the tile doubles as V)
-          { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.o_done[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
-          mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, row + kPrefetch * kBlk);
+          // slot free: S(gk-2) complete (absorb: P.X(gk-3) complete, the tile doubles as V)
+          { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
+          mbar_expect_tx(smem_u32(&sm.k_full[st]), kKTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
-            tma_load_3d(smem_u32(sm.k[st]) + c * Cfg::kSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
+            tma_load_3d(smem_u32(sm.k[st]) + c * kKSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
           if (!kAbsorb) {
             { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
             mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
@@ -198,7 +211,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_qk = make_idesc(kFmt, 0, 0, 128, 128);
+      constexpr uint32_t idesc_qk = make_idesc(kFmt, 0, 0, 128, kBlk);
       constexpr uint32_t idesc_pv = make_idesc(kFmt, 0, 1, 128, D);
       uint32_t gk = 0, qi = 0;
       bool alive = true;
@@ -212,9 +225,10 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const uint32_t q_lo = desc_lo_sw128(smem_u32(sm.q), 16), k_lo = desc_lo_sw128(smem_u32(sm.k[st]), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          constexpr int kSubStep = Cfg::kSubBytes >> 4;
-          const uint32_t off = (kk >> 2) * kSubStep + (kk & 3) * 2;  // in 16-byte units
-          mma_ss2(d_tmem, q_lo + off, k_lo + off, idesc_qk, kk > 0);
+          // in 16-byte units: 64-column sub tiles are a whole sub tile apart, 16 columns are 32 bytes
+          const uint32_t off_q = (kk >> 2) * (Cfg::kSubBytes >> 4) + (kk & 3) * 2;
+          const uint32_t off_k = (kk >> 2) * (kKSubBytes >> 4) + (kk & 3) * 2;
+          mma_ss2(d_tmem, q_lo + off_q, k_lo + off_k, idesc_qk, kk > 0);
         }
         mma_commit(smem_u32(&sm.s_full[g & 1]));
         if (last) mma_commit(smem_u32(&sm.q_free));
@@ -225,7 +239,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         const int idx = wq_consume_thread(sm.wq, n, abort_flag);
         if (idx < 0) break;
         const WorkItem w = p.items[idx];
-        const int nb = (w.i_len + kTile - 1) / kTile;
+        const int nb = (w.i_len + kBlk - 1) / kBlk;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
         tc_fence_after();
@@ -255,13 +269,17 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           if (!kAbsorb) { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.v_full[st]), ph, abort_flag)) { alive = false; break; } TRACE_ADD(6); }
           tc_fence_after();
           const uint32_t a_tmem = tbase + (g & 1) * 128;
-          // V tile: [128 keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles 16 KB apart (the LBO)
-          const uint32_t v_lo = desc_lo_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]), Cfg::kSubBytes);
+          // V tile: [keys][D] as D/64 sub tiles; 16 keys = 2 KB; sub tiles one sub tile apart (the LBO)
+          const uint32_t v_lo = desc_lo_sw128(smem_u32(kAbsorb ? sm.k[st] : sm.v[st]), kKSubBytes);
+          // P: each softmax thread packed its kHalf columns into the first kHalf/2 of them, so K-step kk
+          // (16 keys = 8 packed columns) sits at column (kk / steps_per_half) * kHalf + (kk % steps_per_half) * 8
+          constexpr int kStepsPerHalf = kHalf / 16;
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk >> 2) * 64 + (kk & 3) * 8, v_lo + kk * (2048 >> 4), idesc_pv,
-                    (b > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBlk / 16; ++kk)
+            mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk / kStepsPerHalf) * kHalf + (kk % kStepsPerHalf) * 8, v_lo + kk * (2048 >> 4),
+                    idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
           mma_commit(smem_u32(&sm.o_done[g & 1]));
+          if (kAbsorb) mma_commit(smem_u32(&sm.k_empty[st]));
           if (qk_pending && !issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
         }
         gk += nb;
@@ -286,7 +304,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       const int idx = wq_consume_warp(sm.wq, n, abort_flag);
       if (idx < 0) break;
       const WorkItem w = p.items[idx];
-      const int nb = (w.i_len + kTile - 1) / kTile;
+      const int nb = (w.i_len + kBlk - 1) / kBlk;
       // tile row r -> (query row of the tile, head)
       const int rq = kAbsorb ? r / p.H : r;
       const int h = kAbsorb ? r % p.H : w.head;
@@ -300,35 +318,46 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #ifdef VAFA_TRACE
         const long long t_sm0 = clock64();
 #endif
-        const uint32_t s_addr = lane_base + (g & 1) * 128 + half * 64;
-        float s[64];
-        {
+        const uint32_t s_addr = lane_base + (g & 1) * 128 + half * kHalf;
+        float s[kHalf];
+        if constexpr (kHalf == 64) {
           uint32_t t0[64];
           tmem_ld64(s_addr, t0);
           tmem_wait_ld();
 #pragma unroll
           for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(t0[i]);
-        }
-        // mask: inner index jj = b*128 + col is visible iff jj < i_len and (causal) jj <= r + diag
-        const int lim_tail = w.i_len - 1 - b * kTile;
-        const int lim_diag = w.masked ? (w.diag - b * kTile) : 0x3fffffff;  // for row 0
-        const bool masked_block = lim_tail < kTile - 1 || lim_diag < kTile - 1;  // same for the whole CTA
-        if (masked_block) {
-          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff) - half * 64;
+        } else {
+          static_assert(kHalf == 64 || kHalf == 48, "score columns per thread");
+          uint32_t t0[32], t1[16];
+          tmem_ld32(s_addr, t0);
+          tmem_ld16(s_addr + 32, t1);
+          tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 64; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
+          for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(t0[i]);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) s[32 + i] = __uint_as_float(t1[i]);
+        }
+        // mask: inner index jj = b*kBlk + col is visible iff jj < i_len and (causal) jj <= r + diag
+        const int lim_tail = w.i_len - 1 - b * kBlk;
+        const int lim_diag = w.masked ? (w.diag - b * kBlk) : 0x3fffffff;  // for row 0
+        const bool masked_block = lim_tail < kBlk - 1 || lim_diag < kBlk - 1;  // same for the whole CTA
+        if (masked_block) {
+          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff) - half * kHalf;
+#pragma unroll
+          for (int i = 0; i < kHalf; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
         }
         // row maximum of this half: eight independent chains of 3-input max
         float m8[8];
 #pragma unroll
         for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(s[j2], s[8 + j2], s[16 + j2]);
 #pragma unroll
-        for (int i = 24; i < 56; i += 16) {
+        for (int i = 24; i + 16 <= kHalf; i += 16) {
 #pragma unroll
           for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(m8[j2], s[i + j2], s[i + 8 + j2]);
         }
+        // 24 + 16k columns done; one more group of eight is left for both 64 and 48 columns
 #pragma unroll
-        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = fmaxf(m8[j2], s[56 + j2]);
+        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = fmaxf(m8[j2], s[kHalf - 8 + j2]);
         float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
         // combine with the other half of the row
         sm.xmax[g & 1][half][r] = mx;
@@ -348,11 +377,11 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // the dead-row test (row sum == 0) relies on.
         const uint64_t cs2 = pack_f2(c, c), nm2 = pack_f2(-m_use, -m_use);
         uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
-        uint32_t pk[32];
+        uint32_t pk[kHalf / 2];
         auto exps = [&](auto poly_tag) {
           constexpr bool kPoly = decltype(poly_tag)::value;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < kHalf / 2; ++i) {
             const uint64_t t2 = fma_f2(pack_f2(s[2 * i], s[2 * i + 1]), cs2, nm2);
             float p0, p1;
             if (kPoly && (i % kPolyPeriod == kPolyPeriod - 1)) {
@@ -375,9 +404,19 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           l = l * alpha + ((a0 + a1) + (b0 + b1));
         }
         m_ref = m_new;
-        // 64 probabilities -> 32 packed columns over the first half of the columns just read; the MMA
-        // issuer addresses K-step kk at column (kk/4)*64 + (kk%4)*8
-        tmem_st32(s_addr, pk);
+        // kHalf probabilities -> kHalf/2 packed columns over the first half of the columns just read
+        // (the MMA issuer's addressing of the K-steps is next to its P.V loop)
+        if constexpr (kHalf == 64) {
+          tmem_st32(s_addr, pk);
+        } else {
+          uint32_t pa[16], pb[8];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pa[i] = pk[i];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) pb[i] = pk[16 + i];
+          tmem_st16(s_addr, pa);
+          tmem_st8(s_addr + 16, pb);
+        }
         if (b > 0 && __any_sync(0xffffffffu, resc)) {
 #ifdef VAFA_TRACE
           tr[10] += clock64() - t_sm0;
@@ -690,7 +729,7 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   if (rc) return rc;
   CUtensorMap tu, tx;
   if ((rc = encode_tmap_rows(&tu, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
-  if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, a.x_width, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, a.x_width, fwd_block_keys<true>()))) return rc;
   FwdParams p;
   p.o = a.axn; p.lse = a.lse; p.partial_o = nullptr; p.partial_lse = nullptr;
   p.header = sp.header; p.items = sp.items; p.H = a.H;
