@@ -8,7 +8,7 @@ benchmark configuration 2 (64 sequences, lengths log-uniform in [1, 4096] from a
 H=16, D=128, bf16, causal; synthetic N(0,1) values).  FLOPs use the reference harness's
 convention, 4*H*D*cells for the forward (cells = L(L+1)/2 under the causal mask) and 2.5x
 that for the backward.  With N > 1 (torchrun, one rank per GPU) every rank runs its own batch
-of the same configuration (rank r draws lengths and values from seed r): packed batches shard
+of the same configuration (the same length list on every rank, values from seed r): packed batches shard
 by sequence with no data-path collective, so this is weak scaling and `value` is the sum over
 ranks divided by the slowest rank's time.
 
@@ -129,7 +129,11 @@ class ClockSampler:
 def make_batch(workload: str, seed: int):
     from oracle import CONFIGS, config_lengths
     cfg = CONFIGS[workload]
-    ql, kl = config_lengths(workload, seed)
+    # every rank gets the configuration's own length list (seed 0): weak scaling means the same work per
+    # GPU, and `value` divides by the slowest rank's time, so ranks with different draws of the lengths
+    # (whose cell counts differ by tens of percent) would measure the draw, not the scaling.  The values
+    # differ per rank.
+    ql, kl = config_lengths(workload, 0)
     g = torch.Generator(device="cpu").manual_seed(seed)
     H, D = cfg["H"], cfg["D"]
     dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg["dtype"]]
