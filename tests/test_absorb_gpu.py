@@ -180,3 +180,12 @@ def test_forward_backward_inside_a_cuda_graph():
     torch.cuda.synchronize()
     for name, a, b in zip(("O", "dq_raw", "dX", "dW_Q", "dW_K", "dW_V"), captured, eager):
         assert torch.equal(a, b), name
+
+
+@pytest.mark.parametrize("H,D_H", [(4, 32), (8, 16), (2, 64)])
+def test_head_dims_off_the_fused_projection_path(H, D_H):
+    """d_kv = 256 keeps the tensor-core forward core while H * D_H != 256 sends the output projection, the
+    backward and the weight gradients through the general kernels."""
+    ql, kl = [3, 9, 16, 1], [70, 300, 129, 5]
+    ins, O, grads = _run(ql, kl, 256, 256, H, D_H, torch.bfloat16, 3, x_std=1.0, w_std=None)
+    _compare(ins, O, grads, torch.bfloat16)
