@@ -73,8 +73,9 @@ struct FwdSmem {
   alignas(1024) uint8_t v[kAbsorb ? 1 : FwdCfg<D>::kStages][kAbsorb ? 1024 : FwdCfg<D>::kTileBytes];
   alignas(8) uint64_t q_full, q_free;
   uint64_t k_full[3], v_full[2];
-  uint64_t k_empty[3];  // absorb: slot free again (P.X of its block complete)
-  uint64_t s_full[2], p_full[2], o_done[2];  // indexed by block parity; phase = (block / 2) & 1
+  uint64_t s_full[2], p_full[2];  // indexed by block parity; phase = (block / 2) & 1
+  uint64_t o_done[3];             // P.V of block g complete: index g % stages, phase (g / stages) & 1; it also
+                                  // frees the V slot (absorb: the X slot) of the block
   uint64_t pair_bar[4];       // the two softmax warps of one TMEM lane quadrant
   float xmax[2][2][128];      // [block parity][half][row] partial row maxima
   float xsum[2][128];         // [half][row] partial row sums at the end of an item
@@ -128,13 +129,12 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
     mbar_init(smem_u32(&sm.q_free), 1);
     for (int i = 0; i < S; ++i) {
       mbar_init(smem_u32(&sm.k_full[i]), 1);
-      mbar_init(smem_u32(&sm.k_empty[i]), 1);
+      mbar_init(smem_u32(&sm.o_done[i]), 1);
     }
     for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&sm.v_full[i]), 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&sm.s_full[i]), 1);
       mbar_init(smem_u32(&sm.p_full[i]), 8);  // lane 0 of each softmax warp
-      mbar_init(smem_u32(&sm.o_done[i]), 1);
     }
     fence_barrier_init();
   }
@@ -193,7 +193,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           if (kAbsorb && b + kPrefetch < nb)
             for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, row + kPrefetch * kBlk);
           // slot free: S(gk-2) complete (absorb: P.X(gk-3) complete, the tile doubles as V)
-          { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.k_empty[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.o_done[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.k_full[st]), kKTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
             tma_load_3d(smem_u32(sm.k[st]) + c * kKSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
@@ -278,8 +278,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           for (int kk = 0; kk < kBlk / 16; ++kk)
             mma_ts2(tbase + Cfg::kOCol, a_tmem + (kk / kStepsPerHalf) * kHalf + (kk % kStepsPerHalf) * 8, v_lo + kk * (2048 >> 4),
                     idesc_pv, (b > 0 || kk > 0) ? 1u : 0u);
-          mma_commit(smem_u32(&sm.o_done[g & 1]));
-          if (kAbsorb) mma_commit(smem_u32(&sm.k_empty[st]));
+          mma_commit(smem_u32(&sm.o_done[st]));
           if (qk_pending && !issue_qk(g + 1, b + 2 == nb)) { alive = false; break; }
         }
         gk += nb;
@@ -423,7 +422,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 #endif
           // O may be rescaled once P.V of the previous block is complete (the next one waits for this
           // warp's arrival below).  No alias in the parity wait: S(g) complete implies P.V(g-2) complete.
-          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
+          { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[(g - 1) % S]), ((g - 1) / S) & 1, abort_flag)) { alive = false; break; } TRACE_ADD(9); }
           tc_fence_after();
           {
 #pragma unroll
@@ -452,7 +451,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
       // ---- epilogue ----
       float l_tot = 0.f;
       if (nb > 0) {
-        if (!mbar_wait(smem_u32(&sm.o_done[(gk - 1) & 1]), ((gk - 1) >> 1) & 1, abort_flag)) break;
+        if (!mbar_wait(smem_u32(&sm.o_done[(gk - 1) % S]), ((gk - 1) / S) & 1, abort_flag)) break;
         tc_fence_after();
         sm.xsum[half][r] = l;
         mbar_arrive(pair_bar);
