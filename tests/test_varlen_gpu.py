@@ -228,3 +228,34 @@ def test_sequence_sharding_is_bitwise_equivalent():
                     local_cu_seqlens(L, part, r)) for r in range(world)]
         for i in range(4):
             assert torch.equal(unshard_rows([o[i] for o in outs], L, part), full[i])
+
+
+def test_forward_backward_inside_a_cuda_graph():
+    """With validation off the op neither synchronises nor reads lengths on the host, so a forward+backward
+    (split-K forward included) can be captured into a CUDA graph; the replay reproduces the eager bits."""
+    ql, kl = [300, 45, 128, 1], [300, 9000, 128, 7]
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 4, 128, torch.bfloat16, 6)
+    g = [t.to(DEV).requires_grad_(True) for t in (q, k, v)]
+    cu_q, cu_k, do = cu_q.to(DEV), cu_k.to(DEV), do.to(DEV)
+    vb.set_validate_cu_seqlens(False)
+    try:
+        def step():
+            o = vb.packed_varlen_attn(*g, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+            return (o,) + torch.autograd.grad(o, g, do)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                eager = [t.clone() for t in step()]
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            captured = step()
+        for _ in range(2):
+            graph.replay()
+        torch.cuda.synchronize()
+        for name, a, b in zip(("o", "dq", "dk", "dv"), captured, eager):
+            assert torch.equal(a, b), name
+    finally:
+        vb.set_validate_cu_seqlens(True)
