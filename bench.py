@@ -1,29 +1,38 @@
 #!/usr/bin/env python
-"""Benchmark of the packed variable-length attention hot path (forward + backward).
+"""Benchmark of the two hot paths on the box-scale configuration.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C2]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload C5]
 
-One step = one forward + backward pass of `packed_varlen_attn` over one packed batch of
-benchmark configuration 2 (64 sequences, lengths log-uniform in [1, 4096] from a fixed seed,
-H=16, D=128, bf16, causal; synthetic N(0,1) values).  FLOPs use the reference harness's
-convention, 4*H*D*cells for the forward (cells = L(L+1)/2 under the causal mask) and 2.5x
-that for the backward.  With N > 1 (torchrun, one rank per GPU) every rank runs its own batch
-of the same configuration (the same length list on every rank, values from seed r): packed batches shard
-by sequence with no data-path collective, so this is weak scaling and `value` is the sum over
-ranks divided by the slowest rank's time.
+Default workload, configuration 5 ("C5"): ONE packed batch of 1 000 000 tokens (520 sequences, lengths
+log-uniform in [128, 8192] from a fixed seed, H=32, D=128, bf16, causal) through `packed_varlen_attn`
+forward + backward -- this is `value`, in TFLOP/s -- plus ONE batch of 16 384 users through
+`packed_target_attn` forward + backward, reported under `absorb` in keys/s.  Values are synthetic
+N(0,1), drawn on the device (the host copy of the batch alone would be 33 GB).  FLOPs use the reference
+harness's convention: forward 4*H*D*cells (cells = visible (query, key) pairs, L(L+1)/2 per causal
+sequence), backward 2.5x that.
 
-The JSON line also carries: `e2e` (same metric, host pinned buffers in, host buffers out, copies
-inside the timed region), `roofline` of the dominant kernel (event-timed inside this run),
-`cpu_baseline` (the fp32 torch CPU restatement of the reference's own oracle, timed on a bounded
-sample on this box's host cores), `absorb` (target-attention keys/s on configuration 4 and on the
-production-like shape: forward, forward+backward, and the forward+backward step replayed from a CUDA
-graph, which leaves the host's launch rate out) and the GPU clocks sampled during the timed regions.
+With N > 1 (torchrun, one rank per GPU) the SAME batch is cut by whole sequences with
+`sharding.partition_segments` and each rank runs its shard: strong scaling.  `value` is the whole
+batch's FLOPs divided by the slowest rank's device time.  The varlen path exchanges nothing; the absorb
+operator all-reduces its fp32 weight gradients over NCCL inside the timed step.
+
+The JSON line also carries `e2e` (the same metric through the public API with pinned host buffers in
+and out, copies inside the timed region, on a stated slice of the batch), `roofline` of the dominant
+kernel (event-timed inside this run), `cpu_baseline` (the fp32 torch CPU restatement of the reference's
+own oracle on a bounded sample, N=1 only), `vs_reference_gpu` (N=1 only: the reference's Triton kernels
+and flash-attn timed in a child process on the same GPU and the same seeded inputs, on the shapes their
+32-bit indexing can address) and the GPU clocks sampled during the timed regions.
+
+Other workloads: C2, C2b, S1 (named length generators), `stage1:<row>` (a row of the reference's logged
+production shapes, tests/golden/stage1_shapes.jsonl.gz) for the varlen operator, and `absorb-prod:<i>`
+(record i of tests/golden/real_shape_all.json.gz; d_q=968, d_kv=216) / `C4` for the absorb operator
+alone.
 """
 from __future__ import annotations
 
 import argparse
+import gzip
 import json
-import math
 import os
 import statistics
 import subprocess
@@ -37,16 +46,11 @@ sys.path.insert(0, ROOT)
 import torch  # noqa: E402
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
-
-# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum)
-# from the ncu capture summarised under profiles/ for the same kernel, or None when no capture
-# exists for this workload.
-NCU_TRAFFIC_BYTES = {
-    # profiles/varlen_kernels_C2_ncu_full.md (dram__bytes_read.sum + dram__bytes_write.sum, one launch)
-    ("C2", "varlen_bwd_kernel<dKV>"): 574_531_328 + 231_917_056,
-    ("C2", "varlen_bwd_kernel<dQ>"): 540_098_816 + 116_789_504,
-    ("C2", "varlen_fwd_kernel"): 400_167_424 + 113_049_344,
-}
+GOLDEN = os.path.join(ROOT, "tests", "golden")
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+# matrix products each varlen kernel performs per visible (query, key) cell
+PRODUCTS = {"varlen_fwd_kernel": 2, "varlen_bwd_kernel<dQ>": 3, "varlen_bwd_kernel<dKV>": 4,
+            "varlen_bwd_kernel<fused>": 5}
 
 
 def load_peaks():
@@ -56,6 +60,20 @@ def load_peaks():
             d = json.load(fh)
         return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d}, "measured"
     return dict(FALLBACK_PEAKS), "fallback"
+
+
+def load_dram_traffic():
+    """Rows `| workload | kernel | bytes per launch | tokens |` of profiles/dram_traffic.md: DRAM bytes
+    (read + write) one launch moved in an ncu capture, and the token count of the captured batch."""
+    out = {}
+    path = os.path.join(ROOT, "profiles", "dram_traffic.md")
+    if not os.path.exists(path):
+        return out
+    for line in open(path):
+        f = [x.strip() for x in line.strip().strip("|").split("|")]
+        if len(f) >= 4 and f[2].replace("_", "").isdigit() and f[3].replace("_", "").isdigit():
+            out.setdefault(f[1].strip("`"), []).append((f[0], int(f[2].replace("_", "")), int(f[3].replace("_", ""))))
+    return out
 
 
 def causal_cells(ql, kl):
@@ -126,67 +144,158 @@ class ClockSampler:
                 "samples": len(sm), "power_w_max": max(power)}
 
 
-def make_batch(workload: str, seed: int):
+# ---------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------
+def _golden_lines(name):
+    with gzip.open(os.path.join(GOLDEN, name), "rt", encoding="utf-8") as fh:
+        return fh.read()
+
+
+def stage1_row(i: int):
+    rows = [json.loads(l) for l in _golden_lines("stage1_shapes.jsonl.gz").splitlines() if l.strip()]
+    r = rows[i]
+    return r["name"], [int(x) for x in r["q_lens"]], [int(x) for x in r["k_lens"]]
+
+
+def absorb_prod_record(i: int):
+    rec = json.loads(_golden_lines("real_shape_all.json.gz"))["records"][i]
+    return rec["tag"] + f"#{i}", [int(x) for x in rec["q_lens"]], [int(x) for x in rec["k_lens"]]
+
+
+def workload(name: str) -> dict:
+    """kind 'varlen': q/k lengths + H, D, causal; kind 'absorb': lengths + d_q, d_kv."""
     from oracle import CONFIGS, config_lengths
-    cfg = CONFIGS[workload]
-    # every rank gets the configuration's own length list (seed 0): weak scaling means the same work per
-    # GPU, and `value` divides by the slowest rank's time, so ranks with different draws of the lengths
-    # (whose cell counts differ by tens of percent) would measure the draw, not the scaling.  The values
-    # differ per rank.
-    ql, kl = config_lengths(workload, 0)
-    g = torch.Generator(device="cpu").manual_seed(seed)
-    H, D = cfg["H"], cfg["D"]
-    dt = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[cfg["dtype"]]
-    Tq, Tk = sum(ql), sum(kl)
+    if name == "C5":
+        ql, kl = config_lengths("C5v", 0)
+        c = CONFIGS["C5v"]
+        return dict(kind="varlen", name="C5", ql=ql, kl=kl, H=c["H"], D=c["D"], causal=c["causal"], absorb="C5a",
+                    label="C5: one packed batch, lengths logU[128,8192] seed 0, causal")
+    if name in ("C2", "C2b", "S1", "C3"):
+        ql, kl = config_lengths(name, 0)
+        c = CONFIGS[name]
+        return dict(kind="varlen", name=name, ql=ql, kl=kl, H=c["H"], D=c["D"], causal=c["causal"],
+                    absorb="C4" if name.startswith("C2") else None, label=f"{name}: named length generator, seed 0")
+    if name.startswith("stage1:"):
+        nm, ql, kl = stage1_row(int(name.split(":")[1]))
+        return dict(kind="varlen", name=name, ql=ql, kl=kl, H=4, D=64, causal=False, absorb=None,
+                    label=f"{nm}: logged production shape (q=500 per user, keys up to 102 400)")
+    if name in ("C4", "C5a"):
+        ql, kl = config_lengths(name, 0)
+        return dict(kind="absorb", name=name, ql=ql, kl=kl, d_q=256, d_kv=256, label=f"{name}: q U[1,16], k logU[8,2048]")
+    if name.startswith("absorb-prod:"):
+        nm, ql, kl = absorb_prod_record(int(name.split(":")[1]))
+        return dict(kind="absorb", name=name, ql=ql, kl=kl, d_q=968, d_kv=216, label=f"{nm}: logged production batch")
+    raise SystemExit(f"unknown workload {name}")
 
-    def rnd(T):
-        return torch.randn(T, H, D, generator=g, dtype=torch.float32).to(dt).pin_memory()
-    return cfg, ql, kl, rnd(Tq), rnd(Tk), rnd(Tk), rnd(Tq)
+
+def balanced_partition(ql, kl, world, causal):
+    """Whole sequences to ranks, balancing tokens AND attention cells at once: sequences in descending
+    cell order, each to the rank whose larger normalised load (tokens, cells) stays smallest.  Tokens set
+    the memory and HBM traffic of a shard, cells its tensor-core time."""
+    from varlenabsorbflashattn_b200.sharding import Partition
+    tok = [a + b for a, b in zip(ql, kl)]
+    cel = [cells_of([a], [b], causal) for a, b in zip(ql, kl)]
+    tt, tc = max(1, sum(tok)), max(1, sum(cel))
+    order = sorted(range(len(ql)), key=lambda i: (-cel[i], i))
+    lt, lc = [0] * world, [0] * world
+    owned = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (max((lt[j] + tok[i]) / tt, (lc[j] + cel[i]) / tc), j))
+        owned[r].append(i); lt[r] += tok[i]; lc[r] += cel[i]
+    for o in owned:
+        o.sort()
+    return Partition(owned, lt), lt, lc
 
 
-def cpu_reference_sample(workload: str, budget_cells: float, threads: int):
-    """Time the fp32 torch CPU path (per segment, autograd backward) on a leading sample."""
-    from oracle import CONFIGS, config_lengths, make_varlen_inputs, varlen_attn_ref_fwd_bwd
-    cfg = CONFIGS[workload]
-    ql, kl = config_lengths(workload, 0)
-    tot, n = 0, 0
-    for a, b in zip(ql, kl):
-        if n > 0 and tot + a * b > budget_cells:
+def _imb(load):
+    m = sum(load) / max(1, len(load))
+    return round(max(load) / m, 4) if m > 0 else 1.0
+
+
+def partition_report(ql, kl, world, causal):
+    from varlenabsorbflashattn_b200.sharding import partition_segments
+    cel = lambda a, b: cells_of([a], [b], causal)
+    p_tok = partition_segments(ql, kl, world)
+    p_cel = partition_segments(ql, kl, world, weight=cel)
+    part, lt, lc = balanced_partition(ql, kl, world, causal)
+
+    def both(p):
+        t = [sum(ql[i] + kl[i] for i in seg) for seg in p.assignment]
+        c = [sum(cel(ql[i], kl[i]) for i in seg) for seg in p.assignment]
+        return {"token_imbalance": _imb(t), "cell_imbalance": _imb(c)}
+    return part, {"used": "tokens+cells (vector greedy)", "used_balance": {"token_imbalance": _imb(lt), "cell_imbalance": _imb(lc)},
+                  "token_balanced_lpt": both(p_tok), "cell_balanced_lpt": both(p_cel)}
+
+
+def device_randn(shape, seed, dev, dtype=torch.bfloat16, std=1.0):
+    g = torch.Generator(device=dev)
+    g.manual_seed(int(seed))
+    t = torch.randn(shape, generator=g, device=dev, dtype=dtype)
+    return t if std == 1.0 else t * std
+
+
+def shard_of(full, lens, part, rank, world):
+    if world == 1:
+        return full
+    from varlenabsorbflashattn_b200.sharding import shard_rows
+    return shard_rows(full, lens, part, rank)
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU baseline / reference arm
+# ---------------------------------------------------------------------------------------------
+def cpu_reference_sample(wl: dict, budget_cells: float, threads: int):
+    """Time the fp32 torch CPU path (per segment, autograd backward) on a leading sample of the batch."""
+    from oracle import make_varlen_inputs, varlen_attn_ref_fwd_bwd
+    ql, kl = wl["ql"], wl["kl"]
+    # sequences in batch order, each taken if it still fits the budget of Lq*Lk cells (the oracle computes
+    # the full rectangle, masked or not); at least one sequence (the smallest) is always taken
+    tot, pick = 0, []
+    for i, (a, b) in enumerate(zip(ql, kl)):
+        if tot + a * b <= budget_cells:
+            tot += a * b
+            pick.append(i)
+        if tot >= 0.9 * budget_cells:
             break
-        tot += a * b
-        n += 1
-    ql, kl = ql[:n], kl[:n]
+    if not pick:
+        pick = [min(range(len(ql)), key=lambda i: ql[i] * kl[i])]
+    sq, sk = [ql[i] for i in pick], [kl[i] for i in pick]
+    n = len(pick)
     torch.set_num_threads(threads)
-    q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, cfg["H"], cfg["D"], cfg["dtype"], 0)
+    q, k, v, do, cu_q, cu_k = make_varlen_inputs(sq, sk, wl["H"], wl["D"], "bf16", 0)
     t0 = time.perf_counter()
-    varlen_attn_ref_fwd_bwd(q, k, v, do, cu_q, cu_k, causal=cfg["causal"])
+    varlen_attn_ref_fwd_bwd(q, k, v, do, cu_q, cu_k, causal=wl["causal"])
     dt = time.perf_counter() - t0
-    flops = 3.5 * 4 * cfg["H"] * cfg["D"] * cells_of(ql, kl, cfg["causal"])
-    all_cells = cells_of(*config_lengths(workload, 0), cfg["causal"])
-    frac = cells_of(ql, kl, cfg["causal"]) / max(1, all_cells)
-    return flops / dt / 1e12, dt, f"first {n} of {len(config_lengths(workload, 0)[0])} sequences of {workload} seed 0 ({100 * frac:.0f}% of its cells), fwd+bwd, fp32 torch on CPU"
+    flops = 3.5 * 4 * wl["H"] * wl["D"] * cells_of(sq, sk, wl["causal"])
+    frac = cells_of(sq, sk, wl["causal"]) / max(1, cells_of(ql, kl, wl["causal"]))
+    return flops / dt / 1e12, dt, (f"{n} of the {len(ql)} sequences of {wl['name']} (in batch order, those that fit a budget of "
+                                   f"{budget_cells:.1e} Lq*Lk cells; lengths {min(sq)}-{max(sq)}; {100 * frac:.2f}% of the batch's cells), "
+                                   "fwd+bwd, fp32 torch on CPU")
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank):
     if rank != 0:
         return
+    wl = workload(args.workload)
+    if wl["kind"] != "varlen":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm times the varlen operator's CPU path only"}))
+        return
     threads = os.cpu_count() or 1
-    vals = []
-    sample = ""
+    vals, sample = [], ""
     for i in range(args.warmup + args.steps):
-        v, dt, sample = cpu_reference_sample(args.workload, args.ref_cells, threads)
+        v, dt, sample = cpu_reference_sample(wl, args.ref_cells, threads)
         if i >= args.warmup:
             vals.append((v, dt))
     value = sum(v for v, _ in vals) / len(vals)
     ms = 1e3 * sum(d for _, d in vals) / len(vals)
-    from oracle import CONFIGS
-    cfg = CONFIGS[args.workload]
     line = {
         "impl": "reference", "metric": "varlen-attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: packed varlen {'causal' if cfg['causal'] else 'non-causal'} attention fwd+bwd, H={cfg['H']} D={cfg['D']}",
-                   "note": "reference's torch CPU path (per-segment fp32 matmul-softmax-matmul, autograd backward); each step is a bounded sample"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": varlen_config(wl, 1, None),
+        "note": "the reference's torch CPU path (per-segment fp32 matmul-softmax-matmul, autograd backward) on this "
+                "box's host cores; each step is a bounded leading sample of the workload",
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -194,10 +303,26 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def varlen_config(wl, world, part_info):
+    ql = wl["ql"]
+    mb = sum(ql) * wl["H"] * wl["D"] * 2 / 1e6
+    cfg = {"workload": f"{wl['label']}; packed varlen {'causal' if wl['causal'] else 'non-causal'} attention fwd+bwd, "
+                       f"{len(ql)} sequences, {sum(ql)} tokens, H={wl['H']} D={wl['D']} bf16",
+           "flops_convention": "fwd 4*H*D*cells (visible cells), bwd 2.5x fwd",
+           "l2": f"inputs larger than L2 (q, k, v, dO: {mb:.0f} MB each over the whole batch)",
+           "parallelism": f"dp{world} by whole sequence: one batch cut across ranks, no data-path collective "
+                          "(absorb leg: NCCL all-reduce of the fp32 weight gradients inside the step)"}
+    if part_info is not None:
+        cfg["partition"] = part_info
+    return cfg
+
+
+# ---------------------------------------------------------------------------------------------
+# absorb leg
+# ---------------------------------------------------------------------------------------------
 def production_lengths(seed=0):
-    """Synthetic stand-in for the reference's production length lists (its fixture of 100 logged
-    batches: 1103-1174 users, 2.2-2.35 M keys; 96-98 % of the users have exactly 2048 keys, the rest
-    anything from 1 up; 1-18 queries per user, mean 5.3)."""
+    """Synthetic stand-in with the distribution of the reference's logged production batches
+    (1103-1174 users, 96-98 % of them with exactly 2048 keys, 1-18 queries per user, mean 5.3)."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     n = 1137
     q = torch.clamp((torch.empty(n, dtype=torch.float64).exponential_(1 / 4.8, generator=g)).floor().long() + 1, 1, 18)
@@ -206,87 +331,216 @@ def production_lengths(seed=0):
     return [int(x) for x in q], [int(x) for x in k]
 
 
-def absorb_leg(dev, steps, warmup, group, production=False):
-    """Target attention on configuration 4 (or the production-like shape: d_q = 968, d_kv = 216):
-    keys/s forward and forward+backward."""
-    import varlenabsorbflashattn_b200 as vb
-    from oracle import config_lengths, lengths_to_cu
-    ql, kl = production_lengths(0) if production else config_lengths("C4", 0)
-    d_q, d_kv = (968, 216) if production else (256, 256)
+def absorb_inputs(ql, kl, d_q, d_kv, dev, seed=0):
     Tq, Tk = sum(ql), sum(kl)
-    g = torch.Generator(device="cpu").manual_seed(0)
-    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g) * std).to(torch.bfloat16).to(dev)
-    q_raw, X = mk(Tq, d_q), mk(Tk, d_kv)
-    W = [mk(d, 8, 32, std=1 / 16).requires_grad_(True) for d in (d_q, d_kv, d_kv)]
-    q_raw.requires_grad_(True); X.requires_grad_(True)
-    dO = mk(Tq, 8, 32)
-    cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
+    q_raw = device_randn((Tq, d_q), seed * 16 + 1, dev)
+    X = device_randn((Tk, d_kv), seed * 16 + 2, dev)
+    W = [device_randn((d, 8, 32), seed * 16 + 3 + i, dev, std=1 / 16) for i, d in enumerate((d_q, d_kv, d_kv))]
+    dO = device_randn((Tq, 8, 32), seed * 16 + 6, dev)
+    return q_raw, X, W, dO
+
+
+def absorb_leg(dev, ql, kl, d_q, d_kv, steps, warmup, timed, rank, world, group, label, graph=False, shard_check=False):
+    """packed_target_attn forward and forward+backward on one batch (cut across ranks by whole users):
+    keys/s = keys of the whole batch / slowest rank's time."""
+    import varlenabsorbflashattn_b200 as vb
+    from oracle import lengths_to_cu
+    from varlenabsorbflashattn_b200.sharding import partition_segments, local_cu_seqlens
+    Tk = sum(kl)
+    q_raw, X, W, dO = absorb_inputs(ql, kl, d_q, d_kv, dev)
+    part = partition_segments(ql, kl, world) if world > 1 else None
+    if world > 1:
+        lq = shard_of(q_raw, ql, part, rank, world).contiguous()
+        lx = shard_of(X, kl, part, rank, world).contiguous()
+        ldo = shard_of(dO, ql, part, rank, world).contiguous()
+        cu_q = local_cu_seqlens(ql, part, rank).to(dev)
+        cu_k = local_cu_seqlens(kl, part, rank).to(dev)
+    else:
+        lq, lx, ldo = q_raw, X, dO
+        cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
+    lq.requires_grad_(True); lx.requires_grad_(True)
+    Wg = [w.clone().requires_grad_(True) for w in W]
 
     def fwd():
-        return vb.packed_target_attn(q_raw, X, *W, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, validate=False,
+        return vb.packed_target_attn(lq, lx, *Wg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, validate=False,
                                      weight_grad_group=group)
 
     def fb():
-        torch.autograd.grad(fwd(), (q_raw, X, *W), dO)
+        return torch.autograd.grad(fwd(), (lq, lx, *Wg), ldo)
 
-    out = {}
-    for name, fn in (("fwd", fwd), ("fwd_bwd", fb)):
-        for _ in range(warmup):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        out[name + "_ms"] = ms
-        out[name + "_keys_per_s"] = Tk / (ms * 1e-3)
-    # The same forward+backward replayed from a CUDA graph: a step of this size is some 25 short launches,
-    # so the eager number above contains the host's launch rate; the replay is the device time.
-    if group is None:
+    out = {"workload": label, "unit": "keys/s", "users": len(ql), "queries": sum(ql), "keys": Tk, "d_q": d_q, "d_kv": d_kv}
+    ms_f = timed(lambda: fwd(), steps, warmup)
+    ms_fb = timed(fb, steps, warmup)
+    out.update(fwd_ms=ms_f, fwd_keys_per_s=Tk / (ms_f * 1e-3), fwd_bwd_ms=ms_fb, fwd_bwd_keys_per_s=Tk / (ms_fb * 1e-3))
+    if world > 1:
+        t = [sum(ql[i] + kl[i] for i in seg) for seg in part.assignment]
+        out["partition"] = {"used": "token-balanced LPT by user", "token_imbalance": _imb(t)}
+    if graph and world == 1:
+        # The same step replayed from a CUDA graph: a step of a small batch is some 25 short launches, so the
+        # eager number contains the host's launch rate; the replay is the device time.
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             fb()
         torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
             fb()
-        for _ in range(warmup):
-            graph.replay()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            graph.replay()
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        out["fwd_bwd_graph_ms"] = ms
-        out["fwd_bwd_graph_keys_per_s"] = Tk / (ms * 1e-3)
-    out["workload"] = ("production-like: 1137 users, 97 % with 2048 keys, q 1-18 (mean 5.3), d_q=968, d_kv=216, "
-                       f"H=8, D_H=32, bf16 ({Tq} queries, {Tk} keys)" if production else
-                       "C4: 1024 users, q U[1,16], k logU[8,2048], d=256, H=8, D_H=32, bf16")
-    out["unit"] = "keys/s"
+        ms_g = timed(g.replay, steps, warmup)
+        out.update(fwd_bwd_graph_ms=ms_g, fwd_bwd_graph_keys_per_s=Tk / (ms_g * 1e-3))
+    if shard_check and world > 1:
+        # value check of the sharded operator: the all-reduced weight gradients of the shards against the
+        # whole batch run on this rank alone
+        sh = fb()
+        q_full = q_raw.detach().requires_grad_(True); x_full = X.detach().requires_grad_(True)
+        Wf = [w.clone().requires_grad_(True) for w in W]
+        o = vb.packed_target_attn(q_full, x_full, *Wf, cu_seqlens_q=lengths_to_cu(ql).to(dev),
+                                  cu_seqlens_k=lengths_to_cu(kl).to(dev), validate=False)
+        full = torch.autograd.grad(o, Wf, dO)
+        err = max(float((a.float() - b.float()).abs().max()) for a, b in zip(sh[2:], full))
+        ref = max(float(b.float().abs().max()) for b in full)
+        out["shard_check_max_abs"] = err
+        out["shard_check_max_ref"] = ref
     return out
 
 
+# ---------------------------------------------------------------------------------------------
+# child process: the reference's Triton kernels and flash-attn beside the library, same GPU, same inputs
+# ---------------------------------------------------------------------------------------------
+def compare_leg():
+    res = {}
+    if not os.path.isdir(os.path.join(REF_DIR, "triton_fa_varlen_v2")):
+        print(json.dumps({"unavailable": "baseline/_ref is missing (bash baseline/install_ref.sh installs the reference there)"}))
+        return
+    sys.path.insert(0, REF_DIR)
+    import varlenabsorbflashattn_b200 as vb
+    from oracle import config_lengths, lengths_to_cu
+    vb.set_validate_cu_seqlens(False)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    try:
+        import triton_fa_varlen_v2 as R
+        import triton_target_attn_absorb as RA
+        R.set_validate_cu_seqlens(False)
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"unavailable": f"reference import failed: {str(e)[:160]}"}))
+        return
+    try:
+        from flash_attn import flash_attn_varlen_func
+    except Exception:  # noqa: BLE001
+        flash_attn_varlen_func = None
+
+    def t_ms(fn, n=5, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def ratio(a, b):
+        return {k: round(b[k] / a[k], 3) for k in ("fwd_ms", "fwd_bwd_ms") if k in a and k in b}
+
+    def varlen_case(name, ql, kl, H, D):
+        # every tensor stays far below 2^31 elements: the reference kernels index in 32 bits
+        assert max(sum(ql), sum(kl)) * H * D < 2**31
+        q, k, v, do = (device_randn((T, H, D), 11 + i, dev).requires_grad_(i < 3)
+                       for i, T in enumerate((sum(ql), sum(kl), sum(kl), sum(ql))))
+        cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
+        mq, mk = max(ql), max(kl)
+        impls = {("noncausal", "ours"): lambda: vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k),
+                 ("noncausal", "triton"): lambda: R.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k),
+                 ("causal", "ours"): lambda: vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=True)}
+        if flash_attn_varlen_func is not None:
+            impls[("noncausal", "fa2")] = lambda: flash_attn_varlen_func(q, k, v, cu_q, cu_k, mq, mk, causal=False)
+            impls[("causal", "fa2")] = lambda: flash_attn_varlen_func(q, k, v, cu_q, cu_k, mq, mk, causal=True)
+        out = {}
+        for (mode, who), f in impls.items():
+            try:
+                with torch.no_grad():
+                    tf = t_ms(f)
+                tfb = t_ms(lambda: torch.autograd.grad(f(), (q, k, v), do))
+                out.setdefault(mode, {})[who] = {"fwd_ms": round(tf, 4), "fwd_bwd_ms": round(tfb, 4)}
+            except Exception as e:  # noqa: BLE001
+                out.setdefault(mode, {})[who] = {"error": str(e)[:120]}
+        for mode, d in out.items():
+            fl = 4.0 * H * D * cells_of(ql, kl, mode == "causal")
+            for who, r in d.items():
+                if "fwd_ms" in r:
+                    r["fwd_tflops"] = round(fl / r["fwd_ms"] / 1e9, 1)
+                    r["fwd_bwd_tflops"] = round(3.5 * fl / r["fwd_bwd_ms"] / 1e9, 1)
+            if "ours" in d and "fwd_ms" in d["ours"]:
+                for who in ("triton", "fa2"):
+                    if who in d and "fwd_ms" in d[who]:
+                        d["vs_" + who] = {"fwd": round(d[who]["fwd_ms"] / d["ours"]["fwd_ms"], 3),
+                                          "fwd_bwd": round(d[who]["fwd_bwd_ms"] / d["ours"]["fwd_bwd_ms"], 3)}
+        res[name] = out
+
+    def absorb_case(name, ql, kl, d_q, d_kv):
+        q_raw, X, W, dO = absorb_inputs(ql, kl, d_q, d_kv, dev)
+        q_raw.requires_grad_(True); X.requires_grad_(True)
+        W = [w.requires_grad_(True) for w in W]
+        cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
+        qi, ki = RA.prepare_target_attn_indices(cu_q, cu_k)
+        impls = {"ours": lambda: vb.packed_target_attn(q_raw, X, *W, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, validate=False),
+                 "triton": lambda: RA.packed_target_attn(q_raw, X, *W, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+                                                         q_chunk_indices=qi, k_chunk_indices=ki, validate=False)}
+        out = {}
+        for who, f in impls.items():
+            try:
+                with torch.no_grad():
+                    tf = t_ms(f)
+                tfb = t_ms(lambda: torch.autograd.grad(f(), (q_raw, X, *W), dO))
+                out[who] = {"fwd_ms": round(tf, 4), "fwd_bwd_ms": round(tfb, 4),
+                            "fwd_keys_per_s": sum(kl) / (tf * 1e-3), "fwd_bwd_keys_per_s": sum(kl) / (tfb * 1e-3)}
+            except Exception as e:  # noqa: BLE001
+                out[who] = {"error": str(e)[:120]}
+        if all("fwd_ms" in out.get(w, {}) for w in ("ours", "triton")):
+            out["vs_triton"] = {"fwd": round(out["triton"]["fwd_ms"] / out["ours"]["fwd_ms"], 3),
+                                "fwd_bwd": round(out["triton"]["fwd_bwd_ms"] / out["ours"]["fwd_bwd_ms"], 3)}
+        res[name] = out
+
+    ql, kl = config_lengths("C2", 0)
+    varlen_case("C2", ql, kl, 16, 128)
+    ql, kl = config_lengths("C2b", 0)
+    varlen_case("C2b", ql, kl, 16, 128)
+    ql, kl = config_lengths("C4", 0)
+    absorb_case("C4", ql, kl, 256, 256)
+    ql, kl = production_lengths(0)
+    absorb_case("absorb_production_shape", ql, kl, 968, 216)
+    res["note"] = ("ratios are reference time / this library's time (> 1: this library is faster); the reference has no "
+                   "causal mode, so causal is compared with flash-attn only; shapes whose tensors reach 2^31 elements "
+                   "(C3, C5) are not run on the reference: its 32-bit indexing faulted there")
+    print(json.dumps(res), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="C2")
+    ap.add_argument("--workload", default="C5")
+    ap.add_argument("--leg", default="main", choices=["main", "compare"])
     ap.add_argument("--ref-cells", type=float, default=None,
                     help="cell budget (sum of Lq*Lk) of the CPU sample; default 2.5e7 for the cpu_baseline leg, 6e6 per step for --impl reference")
+    ap.add_argument("--e2e-fraction", type=float, default=0.125,
+                    help="share of the batch's tokens (leading sequences) the end-to-end leg moves through pinned host memory")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-absorb", action="store_true")
+    ap.add_argument("--no-compare", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-groups", type=int, default=8,
                     help="sequence groups (streams) the end-to-end leg overlaps copies and kernels over")
     args = ap.parse_args()
+    if args.leg == "compare":
+        compare_leg()
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
 
     rank = int(os.environ.get("RANK", "0"))
@@ -295,7 +549,7 @@ def main():
 
     if args.impl == "reference":
         args.ref_cells = args.ref_cells or 6e6
-        run_reference(args, rank, world)
+        run_reference(args, rank)
         return
     args.ref_cells = args.ref_cells or 2.5e7
 
@@ -303,6 +557,7 @@ def main():
     import varlenabsorbflashattn_b200 as vb
     from varlenabsorbflashattn_b200 import _lib
     from varlenabsorbflashattn_b200 import build as vbuild
+    from varlenabsorbflashattn_b200.sharding import local_cu_seqlens
     from oracle import lengths_to_cu
 
     if rank == 0:
@@ -317,26 +572,6 @@ def main():
         dist.barrier()
     _lib.load()
     vb.set_validate_cu_seqlens(False)
-
-    cfg, ql, kl, hq, hk, hv, hdo = make_batch(args.workload, rank)
-    causal = cfg["causal"]
-    H, D = cfg["H"], cfg["D"]
-    cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
-    fwd_flops = 4.0 * H * D * cells_of(ql, kl, causal)
-    step_flops = 3.5 * fwd_flops
-
-    q = hq.to(dev).requires_grad_(True)
-    k = hk.to(dev).requires_grad_(True)
-    v = hv.to(dev).requires_grad_(True)
-    do = hdo.to(dev)
-
-    def step():
-        o = vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
-        return (o,) + torch.autograd.grad(o, (q, k, v), do)
-
-    def fwd_only():
-        with torch.no_grad():
-            return vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
 
     def sync_all():
         if world > 1:
@@ -358,92 +593,167 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    def total_over_ranks(x):
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
+    wl = workload(args.workload)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    small_steps = max(3, min(args.steps, 10))
+
+    if wl["kind"] == "absorb":
+        res = absorb_leg(dev, wl["ql"], wl["kl"], wl["d_q"], wl["d_kv"], args.steps, args.warmup, timed, rank, world, group,
+                         wl["label"], graph=True, shard_check=True)
+        _lib.check_status(dev)
+        clocks = sampler.stop() if rank == 0 else None
+        if rank == 0:
+            print(json.dumps({"metric": "absorb target-attn fwd+bwd keys/s", "value": res["fwd_bwd_keys_per_s"], "unit": "keys/s",
+                              "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["fwd_bwd_ms"],
+                              "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                              "data": "synthetic", "config": {"workload": wl["label"]}, "absorb": res, "clocks": clocks}), flush=True)
+        if world > 1:
+            dist.barrier(); dist.destroy_process_group()
+        return
+
+    # ---- the batch, cut across ranks by whole sequences ----
+    ql, kl, H, D, causal = wl["ql"], wl["kl"], wl["H"], wl["D"], wl["causal"]
+    part, part_info = partition_report(ql, kl, world, causal) if world > 1 else (None, None)
+    mine = part.assignment[rank] if world > 1 else list(range(len(ql)))
+    my_ql, my_kl = [ql[i] for i in mine], [kl[i] for i in mine]
+    if world > 1:
+        cu_q, cu_k = local_cu_seqlens(ql, part, rank).to(dev), local_cu_seqlens(kl, part, rank).to(dev)
+    else:
+        cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
+    Tq, Tk = sum(ql), sum(kl)
+    # every rank draws the whole tensor from the same seed and keeps its rows: one batch, whatever N is
+    q = shard_of(device_randn((Tq, H, D), 1, dev), ql, part, rank, world).requires_grad_(True)
+    k = shard_of(device_randn((Tk, H, D), 2, dev), kl, part, rank, world).requires_grad_(True)
+    v = shard_of(device_randn((Tk, H, D), 3, dev), kl, part, rank, world).requires_grad_(True)
+    do = shard_of(device_randn((Tq, H, D), 4, dev), ql, part, rank, world)
+    torch.cuda.empty_cache()
+    fwd_flops = 4.0 * H * D * cells_of(ql, kl, causal)           # the whole batch
+    step_flops = 3.5 * fwd_flops
+    my_cells = cells_of(my_ql, my_kl, causal)
+
+    def step():
+        o = vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
+        return (o,) + torch.autograd.grad(o, (q, k, v), do)
+
+    def fwd_only():
+        with torch.no_grad():
+            return vb.packed_varlen_attn(q, k, v, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
 
     _lib.profile_reset()
     ms_step = timed(step, args.steps, args.warmup)
-    launches = sum(v[2] for v in _lib.profile_read().values())
+    launches = sum(x[2] for x in _lib.profile_read().values())
     launches_per_step = launches // (args.steps + args.warmup)
-    ms_fwd = timed(fwd_only, args.steps, 2)
-    total_flops = total_over_ranks(step_flops)
-    total_fwd_flops = total_over_ranks(fwd_flops)
-    value = total_flops / (ms_step * 1e-3) / 1e12
-    fwd_value = total_fwd_flops / (ms_fwd * 1e-3) / 1e12
-
-    # ---- end to end: pinned host -> device, fwd+bwd through the public API, results -> host.
-    # Sequences are independent, so the batch is cut into contiguous groups of sequences, each on its
-    # own stream: the copy of one group (either direction) runs while another group computes, and the
-    # two copy directions run at the same time.  Every byte of the step's inputs and results still
-    # crosses the bus inside the timed region.
-    ho = torch.empty_like(hq).pin_memory()
-    hdq, hdk, hdv = torch.empty_like(hq).pin_memory(), torch.empty_like(hk).pin_memory(), torch.empty_like(hv).pin_memory()
-    dq_ = torch.empty_like(q.detach()); dk_ = torch.empty_like(k.detach()); dv_ = torch.empty_like(v.detach()); ddo_ = torch.empty_like(do)
-    n_groups = max(1, min(args.e2e_groups, len(ql)))
-    groups = []
-    tot_q, seq0, tq0, tk0 = sum(ql), 0, 0, 0
-    for gi in range(n_groups):
-        seq1, tq1, tk1 = seq0, tq0, tk0
-        target = tot_q * (gi + 1) / n_groups
-        while seq1 < len(ql) and (tq1 < target or gi == n_groups - 1):
-            tq1 += ql[seq1]; tk1 += kl[seq1]; seq1 += 1
-        if seq1 > seq0:
-            groups.append({"q": (tq0, tq1), "k": (tk0, tk1), "stream": torch.cuda.Stream(device=dev),
-                           "cu_q": lengths_to_cu(ql[seq0:seq1]).to(dev), "cu_k": lengths_to_cu(kl[seq0:seq1]).to(dev)})
-        seq0, tq0, tk0 = seq1, tq1, tk1
-
-    def e2e_step():
-        cur = torch.cuda.current_stream()
-        for g in groups:
-            st = g["stream"]
-            st.wait_stream(cur)
-            (q0, q1), (k0, k1) = g["q"], g["k"]
-            with torch.cuda.stream(st):
-                a, b, c, d = dq_[q0:q1], dk_[k0:k1], dv_[k0:k1], ddo_[q0:q1]
-                a.copy_(hq[q0:q1], non_blocking=True); b.copy_(hk[k0:k1], non_blocking=True)
-                c.copy_(hv[k0:k1], non_blocking=True); d.copy_(hdo[q0:q1], non_blocking=True)
-                a = a.detach().requires_grad_(True); b = b.detach().requires_grad_(True); c = c.detach().requires_grad_(True)
-                o = vb.packed_varlen_attn(a, b, c, cu_seqlens_q=g["cu_q"], cu_seqlens_k=g["cu_k"], causal=causal)
-                ga, gb, gc = torch.autograd.grad(o, (a, b, c), d)
-                ho[q0:q1].copy_(o.detach(), non_blocking=True); hdq[q0:q1].copy_(ga, non_blocking=True)
-                hdk[k0:k1].copy_(gb, non_blocking=True); hdv[k0:k1].copy_(gc, non_blocking=True)
-        for g in groups:
-            cur.wait_stream(g["stream"])
-
-    e2e_steps = max(3, min(args.steps, 10))
-    ms_e2e = timed(e2e_step, e2e_steps, 2)
-    e2e_value = total_flops / (ms_e2e * 1e-3) / 1e12
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo))
-    d2h = sum(t.numel() * t.element_size() for t in (ho, hdq, hdk, hdv))
+    ms_fwd = timed(fwd_only, small_steps, 2)
+    value = step_flops / (ms_step * 1e-3) / 1e12
+    fwd_value = fwd_flops / (ms_fwd * 1e-3) / 1e12
 
     # ---- per-kernel durations (events around every launch) for the roofline of the top kernel
     _lib.profile_reset()
     _lib.profile_enable(True)
-    for _ in range(max(3, min(args.steps, 10))):
+    for _ in range(3):
         step()
     torch.cuda.synchronize()
     prof = _lib.profile_read()
     _lib.profile_enable(False)
-    clocks = sampler.stop() if rank == 0 else None
+    _lib.profile_reset()
+    del q, k, v, do
+    torch.cuda.empty_cache()
 
+    # ---- end to end: pinned host -> device, fwd+bwd through the public API, results -> host, on the leading
+    # sequences that hold --e2e-fraction of the tokens (the whole batch is 33 GB each way per step).  The
+    # slice is cut across ranks like the batch.  Sequences are independent, so a rank's share is cut into
+    # groups of sequences, each on its own stream: one group's copies (either direction) run under another
+    # group's kernels.  Every byte of the slice's inputs and results crosses the bus inside the timed region.
+    e2e = None
+    if not args.no_e2e:
+        n_e2e, acc = 0, 0
+        for a in ql:
+            if n_e2e > 0 and acc + a > args.e2e_fraction * Tq:
+                break
+            acc += a; n_e2e += 1
+        eq, ek = ql[:n_e2e], kl[:n_e2e]
+        epart = balanced_partition(eq, ek, world, causal)[0] if world > 1 else None
+        emine = epart.assignment[rank] if world > 1 else list(range(n_e2e))
+        mq, mk = [eq[i] for i in emine], [ek[i] for i in emine]
+        g = torch.Generator(device="cpu").manual_seed(100 + rank)
+        hq, hk, hv, hdo = (torch.randn(T, H, D, generator=g, dtype=torch.float32).to(torch.bfloat16).pin_memory()
+                           for T in (sum(mq), sum(mk), sum(mk), sum(mq)))
+        ho, hdq, hdk, hdv = (torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv))
+        dq_, dk_, dv_, ddo_ = (torch.empty(t.shape, dtype=t.dtype, device=dev) for t in (hq, hk, hv, hdo))
+        n_groups = max(1, min(args.e2e_groups, len(mq)))
+        groups, tot_q, s0, tq0, tk0 = [], sum(mq), 0, 0, 0
+        for gi in range(n_groups):
+            s1, tq1, tk1 = s0, tq0, tk0
+            target = tot_q * (gi + 1) / n_groups
+            while s1 < len(mq) and (tq1 < target or gi == n_groups - 1):
+                tq1 += mq[s1]; tk1 += mk[s1]; s1 += 1
+            if s1 > s0:
+                groups.append({"q": (tq0, tq1), "k": (tk0, tk1), "stream": torch.cuda.Stream(device=dev),
+                               "cu_q": lengths_to_cu(mq[s0:s1]).to(dev), "cu_k": lengths_to_cu(mk[s0:s1]).to(dev)})
+            s0, tq0, tk0 = s1, tq1, tk1
+
+        def e2e_step():
+            cur = torch.cuda.current_stream()
+            for gr in groups:
+                st = gr["stream"]
+                st.wait_stream(cur)
+                (q0, q1), (k0, k1) = gr["q"], gr["k"]
+                with torch.cuda.stream(st):
+                    a, b, c, d = dq_[q0:q1], dk_[k0:k1], dv_[k0:k1], ddo_[q0:q1]
+                    a.copy_(hq[q0:q1], non_blocking=True); b.copy_(hk[k0:k1], non_blocking=True)
+                    c.copy_(hv[k0:k1], non_blocking=True); d.copy_(hdo[q0:q1], non_blocking=True)
+                    a = a.detach().requires_grad_(True); b = b.detach().requires_grad_(True); c = c.detach().requires_grad_(True)
+                    o = vb.packed_varlen_attn(a, b, c, cu_seqlens_q=gr["cu_q"], cu_seqlens_k=gr["cu_k"], causal=causal)
+                    ga, gb, gc = torch.autograd.grad(o, (a, b, c), d)
+                    ho[q0:q1].copy_(o.detach(), non_blocking=True); hdq[q0:q1].copy_(ga, non_blocking=True)
+                    hdk[k0:k1].copy_(gb, non_blocking=True); hdv[k0:k1].copy_(gc, non_blocking=True)
+            for gr in groups:
+                cur.wait_stream(gr["stream"])
+
+        ms_e2e = timed(e2e_step, small_steps, 2)
+        e2e_flops = 3.5 * 4.0 * H * D * cells_of(eq, ek, causal)
+
+        def total(x):
+            t = torch.tensor([float(x)], device=dev, dtype=torch.float64)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            return int(t.item())
+        h2d = total(sum(t.numel() * t.element_size() for t in (hq, hk, hv, hdo)))
+        d2h = total(sum(t.numel() * t.element_size() for t in (ho, hdq, hdk, hdv)))
+        e2e = {"value": e2e_flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "sequence_groups_per_rank": len(groups),
+               "config": f"the first {n_e2e} sequences of the batch ({sum(eq)} tokens, {100 * sum(eq) / Tq:.1f}% of its tokens), "
+                         f"cut across {world} rank(s); host buffers pinned; bytes are summed over ranks"}
+        del hq, hk, hv, hdo, ho, hdq, hdk, hdv, dq_, dk_, dv_, ddo_
+        torch.cuda.empty_cache()
+
+    # ---- absorb operator
     absorb = None
-    if not args.no_absorb:
+    if not args.no_absorb and wl.get("absorb"):
+        from oracle import config_lengths
         try:
-            absorb = absorb_leg(dev, max(3, min(args.steps, 10)), 3, group)
+            name = wl["absorb"]
+            aq, ak = config_lengths(name, 0)
+            absorb = absorb_leg(dev, aq, ak, 256, 256, small_steps, 3, timed, rank, world, group,
+                                f"{name}: {len(aq)} users, q U[1,16], k logU[8,2048], d=256, H=8, D_H=32, bf16; one batch cut "
+                                f"across {world} rank(s) by whole users", graph=True, shard_check=True)
         except Exception as e:  # the headline line must still print
-            absorb = {"error": str(e)[:200]}
-        try:
-            absorb["production_shape"] = absorb_leg(dev, max(3, min(args.steps, 10)), 3, group, production=True)
-        except Exception as e:
-            absorb["production_shape"] = {"error": str(e)[:200]}
+            absorb = {"error": str(e)[:300]}
+        if world == 1:
+            for key, (lens, dq_, dkv_, label) in {
+                    "C4": (config_lengths("C4", 0), 256, 256, "C4: 1024 users, q U[1,16], k logU[8,2048], d=256, H=8, D_H=32, bf16"),
+                    "production_shape": (production_lengths(0), 968, 216,
+                                         "production-like: 1137 users, 97 % with 2048 keys, q 1-18 (mean 5.3), d_q=968, d_kv=216, H=8, D_H=32, bf16")}.items():
+                if key == wl["absorb"]:
+                    continue
+                try:
+                    absorb[key] = absorb_leg(dev, lens[0], lens[1], dq_, dkv_, small_steps, 3, timed, rank, world, group, label, graph=True)
+                except Exception as e:  # noqa: BLE001
+                    absorb[key] = {"error": str(e)[:300]}
     _lib.check_status(dev)
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
         peaks, peak_src = load_peaks()
@@ -451,40 +761,47 @@ def main():
         share = {n: ms for n, (ms, nt, na) in prof.items()}
         tot_ms = sum(share.values()) or 1.0
         top = max(share, key=share.get)
-        cells = cells_of(ql, kl, causal)
-        # matmul FLOPs each kernel performs on the visible cells: 2*D per cell per product
-        products = {"varlen_fwd_kernel": 2, "varlen_bwd_kernel<dQ>": 3, "varlen_bwd_kernel<dKV>": 4}
         roofline = None
-        if top in products:
-            algo = products[top] * 2.0 * H * D * cells
+        if top in PRODUCTS:
+            algo = PRODUCTS[top] * 2.0 * H * D * my_cells      # this rank's launch
             ach = algo / (kern[top] * 1e-3) / 1e12
             peak = peaks["bf16_tflops_sustained"]
+            traffic, traffic_note = None, "no ncu capture on file for this kernel"
+            rows = load_dram_traffic().get(top)
+            if rows:
+                src, nbytes, toks = rows[-1]
+                traffic = int(nbytes * (sum(my_ql) / toks))
+                traffic_note = (f"ncu capture of {src} ({toks} tokens, H={H}): {nbytes} bytes per launch, scaled by tokens "
+                                f"to this launch ({sum(my_ql)} tokens)")
             roofline = {"bound": "tensor", "kernel": top, "achieved": ach, "peak": peak, "unit": "TFLOP/s",
-                        "frac": ach / peak, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, top)),
+                        "frac": ach / peak, "traffic": traffic, "traffic_source": traffic_note,
                         "peak_source": f"{peak_src} sustained bf16 (kernel timed inside a long step)",
                         "avg_launch_ms": kern[top], "share_of_step": share[top] / tot_ms,
                         "algorithmic_flops_per_launch": algo,
-                        "kernel_shares": {n: round(v / tot_ms, 4) for n, v in sorted(share.items(), key=lambda x: -x[1])}}
+                        "step_frac": value / world / peak,
+                        "kernel_shares": {n: round(x / tot_ms, 4) for n, x in sorted(share.items(), key=lambda x: -x[1])}}
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            v_cpu, dt_cpu, sample = cpu_reference_sample(args.workload, args.ref_cells, threads)
-            cpu = {"value": v_cpu, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
-                   "seconds": dt_cpu}
+            v_cpu, dt_cpu, sample = cpu_reference_sample(wl, args.ref_cells, threads)
+            cpu = {"value": v_cpu, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample, "seconds": dt_cpu}
+        compare = None
+        if world == 1 and not args.no_compare:
+            try:
+                r = subprocess.run([sys.executable, os.path.abspath(__file__), "--leg", "compare"], capture_output=True,
+                                   text=True, timeout=900)
+                last = [l for l in r.stdout.splitlines() if l.startswith("{")]
+                compare = json.loads(last[-1]) if last else {"unavailable": (r.stderr or "no output")[-300:]}
+            except Exception as e:  # noqa: BLE001
+                compare = {"unavailable": str(e)[:300]}
         line = {
             "metric": "varlen-attn fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: packed varlen {'causal' if causal else 'non-causal'} attention fwd+bwd, {len(ql)} sequences/rank, "
-                                   f"{sum(ql)} tokens/rank, H={H} D={D} bf16",
-                       "flops_convention": "fwd 4*H*D*cells (visible cells), bwd 2.5x fwd",
-                       "l2": "inputs larger than L2 (q, dO, o, dq: %.0f MB each; k, v, dk, dv: %.0f MB each)" % (hq.numel() * 2 / 1e6, hk.numel() * 2 / 1e6),
-                       "parallelism": f"dp{world} by sequence, no data-path collective"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": varlen_config(wl, world, part_info),
             "fwd_only": {"value": fwd_value, "unit": "TFLOP/s", "ms": ms_fwd},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "sequence_groups": len(groups),
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": int(launches_per_step * args.steps),
-            "roofline": roofline, "cpu_baseline": cpu, "absorb": absorb, "clocks": clocks,
+            "e2e": e2e, "gpu_launches": int(launches_per_step * args.steps),
+            "roofline": roofline, "cpu_baseline": cpu, "absorb": absorb, "vs_reference_gpu": compare, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -103,7 +103,12 @@ int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream);
  * batch.  This entry point takes the same arguments as vafa_varlen_fwd but ignores `workspace`
  * and `workspace_bytes`: its tile lists and split-K partials live in a fixed
  * VAFA_NOALLOC_SCRATCH_BYTES array inside the library's device image (each GPU that loads the
- * library holds that much until the process exits).  It calls no allocation routine of any kind.
+ * library holds that much until the process exits).  The call itself runs no allocation routine
+ * (no cudaMalloc, no cudaFree, no allocating library call).  The array is part of the library's device
+ * code: the CUDA runtime creates it when it loads that code onto a GPU, which with the default lazy
+ * module loading happens at the first call of this library on that GPU (or at start-up with
+ * CUDA_MODULE_LOADING=EAGER).  A host with a frozen memory plan should therefore make one call per GPU
+ * during its own set-up, before the plan is frozen.
  *   - tcgen05 shapes only (bf16/fp16, head_dim 64 or 128); others return VAFA_ERR_UNSUPPORTED.
  *   - Batches whose tile lists do not fit return VAFA_ERR_WORKSPACE with the sizes in the error
  *     text; the split-K partial area shrinks to whatever room is left, so long-KV batches may
@@ -161,6 +166,16 @@ size_t vafa_absorb_bwd_workspace_bytes(const vafa_absorb_args* a);
 int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream);
 int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream);
 
+/* The backward in two calls, for data-parallel callers that all-reduce the weight gradients:
+ *   phase 1 writes everything `dw` depends on (and nothing of dx / dq_raw), phase 2 the rest, so the
+ *   caller can start its collective on `dw` after phase 1 and let it run under phase 2.
+ *   phase 0 is vafa_absorb_bwd.  Both calls take the same arguments and the same workspace, whose
+ *   contents must survive from phase 1 to phase 2.  Shapes that do not run on the tensor-core chain do
+ *   all their work in phase 1; phase 2 is then a no-op.  The reference has no counterpart (it is
+ *   single-GPU; its weight gradients come from torch autograd,
+ *   triton_target_attn_absorb/triton_target_attn_absorb/interface.py:430-435). */
+int vafa_absorb_bwd_phase(const vafa_absorb_args* a, int32_t phase, vafa_stream_t stream);
+
 /* Inner entry on a pre-projected u [T_q, H, d_kv] (q_raw = u, w_q/w_k unused): stands in for
  * target_attn_inner (triton_target_attn_absorb/triton_target_attn_absorb/interface.py:324-354).
  * Backward writes du into dq_raw ([T_q, H, d_kv]), dX into dx and fp32 dW_V into dw. */
@@ -178,6 +193,19 @@ const char* vafa_last_error(void);           /* thread-local text of the last fa
 /* Copy the status word to the host (synchronises `stream`) and translate it: returns 0 or
  * VAFA_ERR_DEVICE with the text available from vafa_last_error(). */
 int vafa_check_status(const int32_t* status, vafa_stream_t stream);
+
+/* ---- failure detection ---------------------------------------------------------------------
+ * No counterpart in the reference (its Triton kernels have no device-side waits).  Every wait inside
+ * the kernels of this library (mbarrier spins of the TMA / MMA / element-wise roles) gives up after a
+ * clock-cycle limit: the CTA raises a shared abort flag, all its roles leave, code 1 with the kernel's
+ * site id goes to the status word, tensor memory is released and the kernel returns.  Nothing traps.
+ * vafa_set_wait_limit_cycles() sets that limit for all later launches of the process (values <= 0 only
+ * read it) and returns the previous one; the default is 4e9 cycles, about two seconds.  The limit is
+ * rounded up to a multiple of 65536 cycles.
+ * vafa_selftest_bounded_wait() launches one CTA that waits, through the same code, on an mbarrier that
+ * nobody arrives on: with the current limit it must come back with code 1, site 900 in `status`. */
+long long vafa_set_wait_limit_cycles(long long cycles);
+int vafa_selftest_bounded_wait(int32_t* status, vafa_stream_t stream);
 
 /* ---- optional per-kernel timing and launch counters -------------------------------------
  * Not part of the reference's interface; it covers what the reference's developer tools do with

@@ -189,3 +189,42 @@ def test_head_dims_off_the_fused_projection_path(H, D_H):
     ql, kl = [3, 9, 16, 1], [70, 300, 129, 5]
     ins, O, grads = _run(ql, kl, 256, 256, H, D_H, torch.bfloat16, 3, x_std=1.0, w_std=None)
     _compare(ins, O, grads, torch.bfloat16)
+
+
+@pytest.mark.parametrize("H,D_H", [(4, 32), (8, 16), (2, 64)])
+def test_narrow_x_off_the_fused_backward_path(H, D_H):
+    """d_kv = 216 with head layouts whose backward does not run on the tensor-core dU/dX kernels: the
+    forward may take X at its own width, the backward needs full-width rows, so the wrapper has to pad X
+    for these layouts.  Forward and backward against the oracle."""
+    ins, O, grads = _run([5, 9, 3], [100, 33, 260], 512, 216, H, D_H, torch.bfloat16, 3)
+    _compare(ins, O, grads, torch.bfloat16)
+
+
+def test_weight_grad_group_path_matches_the_plain_backward():
+    """packed_target_attn(weight_grad_group=pg) cuts its backward in two library calls around the
+    all-reduce of the fp32 weight gradients.  With a one-rank group the sum is the identity, so all five
+    gradients must equal those of the plain call bit for bit."""
+    import torch.distributed as dist
+    import tempfile
+    ql, kl = uniform_lengths(64, 1, 16, 0), log_uniform_lengths(64, 8, 2048, 1)
+    ins = make_absorb_inputs(ql, kl, 256, 256, 8, 32, torch.bfloat16, 0)
+    q_raw, X, W_Q, W_K, W_V, dO, cu_q, cu_k = ins
+    created = False
+    if not dist.is_initialized():
+        store = tempfile.mktemp(prefix="vafa_pg_")
+        dist.init_process_group("nccl", init_method=f"file://{store}", rank=0, world_size=1,
+                                device_id=torch.device("cuda", 0))
+        created = True
+    try:
+        outs = []
+        for group in (None, dist.group.WORLD):
+            g = [t.to(DEV).requires_grad_(True) for t in (q_raw, X, W_Q, W_K, W_V)]
+            O = vb.packed_target_attn(*g, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, weight_grad_group=group)
+            O.backward(dO.to(DEV))
+            torch.cuda.synchronize()
+            outs.append([O] + [t.grad for t in g])
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
+    finally:
+        if created:
+            dist.destroy_process_group()

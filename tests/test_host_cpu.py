@@ -1,5 +1,7 @@
 """Host-side argument handling of the two public wrappers (no GPU): the same exception
 types as the reference for the same mistakes."""
+import os
+
 import pytest
 import torch
 
@@ -113,3 +115,41 @@ def test_absorb_padding_of_production_widths():
     assert torch.equal(Wp[:5], W) and Wp[5:].abs().sum() == 0 and Xp[:, 5:].abs().sum() == 0
     (Wp.sum() * 2 + Xp.sum() * 3).backward()
     assert W.grad.shape == W.shape and torch.all(W.grad == 2) and torch.all(X.grad == 3)
+
+
+def test_production_shape_fixtures_load_and_are_consistent():
+    """The reference's two logged-shape fixtures (stage-1 varlen shapes; production absorb batches), stored
+    gzip-compressed beside the golden vectors, as bench.py's `stage1:<row>` / `absorb-prod:<i>` workloads
+    read them.  Same consistency rules as the reference's loaders
+    (tools/benchmark_packed_varlen_flash_attn.py:900-954; triton_target_attn_absorb/test_smoke.py:502-534)."""
+    import gzip
+    import json
+    import bench
+    gd = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    rows = [json.loads(l) for l in gzip.open(os.path.join(gd, "stage1_shapes.jsonl.gz"), "rt") if l.strip()]
+    assert len(rows) == 958
+    for r in rows:
+        assert r["users"] == len(r["q_lens"]) == len(r["k_lens"])
+        assert r["tq"] == sum(r["q_lens"]) and r["tk"] == sum(r["k_lens"])
+        assert min(r["q_lens"]) > 0 and min(r["k_lens"]) > 0
+    recs = json.load(gzip.open(os.path.join(gd, "real_shape_all.json.gz"), "rt"))["records"]
+    assert len(recs) == 100
+    for r in recs:
+        assert r["n_seg"] == len(r["q_lens"]) == len(r["k_lens"])
+        assert r["sum_q"] == sum(r["q_lens"]) and r["sum_k"] == sum(r["k_lens"])
+        assert r["raw_q_shape"][-1] == 968 and r["raw_k_shape"][-1] == 216
+    w = bench.workload("stage1:0")
+    assert w["kind"] == "varlen" and sum(w["ql"]) == rows[0]["tq"] and w["H"] == 4 and w["D"] == 64
+    w = bench.workload("absorb-prod:99")
+    assert w["kind"] == "absorb" and sum(w["kl"]) == recs[99]["sum_k"] and (w["d_q"], w["d_kv"]) == (968, 216)
+
+
+def test_bench_partition_balances_tokens_and_cells():
+    import bench
+    w = bench.workload("C5")
+    assert sum(w["ql"]) == 1_000_000 and len(w["ql"]) == 520
+    for n in (2, 4, 8):
+        part, info = bench.partition_report(w["ql"], w["kl"], n, True)
+        owned = sorted(i for seg in part.assignment for i in seg)
+        assert owned == list(range(520))                       # every sequence exactly once, none split
+        assert info["used_balance"]["token_imbalance"] <= 1.01 and info["used_balance"]["cell_imbalance"] <= 1.01

@@ -259,3 +259,60 @@ def test_forward_backward_inside_a_cuda_graph():
             assert torch.equal(a, b), name
     finally:
         vb.set_validate_cu_seqlens(True)
+
+
+def test_nan_in_q_reaches_o_lse_and_dq():
+    """A NaN must not vanish: the reference's kernels propagate it through the softmax, so a diverged run
+    shows.  One NaN in a query row makes that row of O, its LSE and its dQ row NaN; the other rows of
+    the segment stay finite in O."""
+    V.set_impl("tcgen05")
+    try:
+        ql, kl = [200, 64], [200, 300]
+        q, k, v, do, cu_q, cu_k = make_varlen_inputs(ql, kl, 2, 128, torch.bfloat16, 5)
+        q[37, 1, 5] = float("nan")
+        qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+        o, lse = vb.packed_varlen_attn_with_lse(qg, kg, vg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+        o.backward(do.to(DEV))
+        assert torch.isnan(o[37, 1]).all() and torch.isnan(lse[37, 1])
+        assert torch.isnan(qg.grad[37, 1]).all()
+        others = torch.ones(o.shape[0], dtype=torch.bool, device=DEV)
+        others[37] = False
+        assert torch.isfinite(o[others].float()).all() and torch.isfinite(o[37, 0].float()).all()
+    finally:
+        V.set_impl("auto")
+
+
+def test_bounded_wait_runs_out_and_is_reported():
+    """Failure detection without a fault: with the wait limit at about a million cycles, a CTA that waits on
+    a barrier nobody arrives on comes back by itself, the status word reads code 1 at the self-test's site,
+    vafa_check_status turns that into VAFA_ERR_DEVICE, and the next ordinary call works."""
+    import ctypes as C
+    from varlenabsorbflashattn_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    prev = lib.vafa_set_wait_limit_cycles(1_000_000)
+    try:
+        st = torch.zeros(4, dtype=torch.int32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        assert lib.vafa_selftest_bounded_wait(st.data_ptr(), stream) == 0
+        rc = lib.vafa_check_status(st.data_ptr(), stream)
+        assert rc == -5, lib.vafa_last_error()
+        host = st.cpu().tolist()
+        assert host[0] == 1 and host[1] == 900, host
+        assert b"bounded wait" in lib.vafa_last_error()
+    finally:
+        assert lib.vafa_set_wait_limit_cycles(prev) >= 1_000_000
+    assert lib.vafa_set_wait_limit_cycles(0) == prev  # reads back, sets nothing
+    ins, o, lse, grads = _run([130, 7], [130, 260], 2, 128, torch.bfloat16, True)
+    _compare(ins, o, lse, grads, torch.bfloat16, True)
+    _lib.check_status(dev)
+
+
+def test_status_check_after_every_call_is_opt_in():
+    from varlenabsorbflashattn_b200 import _lib
+    _lib.set_check_status(True)
+    try:
+        ins, o, lse, grads = _run([70], [90], 2, 64, torch.bfloat16, False)
+        _compare(ins, o, lse, grads, torch.bfloat16, False)
+    finally:
+        _lib.set_check_status(False)

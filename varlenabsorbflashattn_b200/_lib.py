@@ -26,9 +26,9 @@ EXPORTS = (
     "vafa_varlen_fwd_workspace_bytes", "vafa_varlen_bwd_workspace_bytes", "vafa_varlen_fwd", "vafa_varlen_bwd",
     "vafa_varlen_fwd_noalloc",
     "vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes",
-    "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
+    "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_bwd_phase", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
     "vafa_profile_enable", "vafa_profile_kernel_count", "vafa_profile_kernel_name", "vafa_profile_read",
-    "vafa_profile_reset",
+    "vafa_profile_reset", "vafa_set_wait_limit_cycles", "vafa_selftest_bounded_wait",
 )
 
 
@@ -93,6 +93,12 @@ def load() -> C.CDLL:
         for name in ("vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd"):
             getattr(lib, name).argtypes = [C.POINTER(AbsorbArgs), C.c_void_p]
             getattr(lib, name).restype = C.c_int
+        lib.vafa_absorb_bwd_phase.argtypes = [C.POINTER(AbsorbArgs), C.c_int32, C.c_void_p]
+        lib.vafa_absorb_bwd_phase.restype = C.c_int
+        lib.vafa_set_wait_limit_cycles.argtypes = [C.c_longlong]
+        lib.vafa_set_wait_limit_cycles.restype = C.c_longlong
+        lib.vafa_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_void_p]
+        lib.vafa_selftest_bounded_wait.restype = C.c_int
         lib.vafa_profile_enable.argtypes = [C.c_int]
         lib.vafa_profile_kernel_name.argtypes = [C.c_int]
         lib.vafa_profile_kernel_name.restype = C.c_char_p
@@ -144,6 +150,28 @@ def check_status(device: torch.device) -> None:
         msg = last_error()
         st.zero_()
         raise RuntimeError(f"device-side error: {msg}")
+
+
+_check_after_each_op = os.environ.get("VAFA_CHECK_STATUS", "0").lower() in ("1", "true", "on", "yes")
+
+
+def set_check_status(enabled: bool) -> None:
+    """Read the device status word after every operator call (off by default; also VAFA_CHECK_STATUS=1).
+
+    The kernels report device-side failures -- a bounded wait that ran out, a tile list that did not fit
+    its buffers -- by writing a code to a status word instead of trapping, and the outputs of such a call
+    are undefined.  Reading the word needs a stream synchronisation, which is why it is opt-in: with it on,
+    every `packed_varlen_attn` / `packed_target_attn` call (forward and backward) synchronises and raises
+    RuntimeError on a reported failure, much as the reference's cu_seqlens validation synchronises.  With it
+    off, call `check_status(device)` yourself at a point where a synchronisation is acceptable (once per
+    step, say)."""
+    global _check_after_each_op
+    _check_after_each_op = bool(enabled)
+
+
+def maybe_check_status(device: torch.device) -> None:
+    if _check_after_each_op:
+        check_status(device)
 
 
 def workspace(nbytes: int, device: torch.device) -> torch.Tensor | None:

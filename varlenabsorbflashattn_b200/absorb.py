@@ -138,6 +138,7 @@ class _PackedTargetAttn(torch.autograd.Function):
             ws = _lib.workspace(lib.vafa_absorb_fwd_workspace_bytes(a), dev)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_absorb_fwd(a, _stream()), "vafa_absorb_fwd")
+            _lib.maybe_check_status(dev)
         ctx.save_for_backward(q_raw, X, W_Q, W_K, W_V, O, lse, cu_q, cu_k, saved)
         ctx.scale, ctx.group = scale, group
         ctx.mark_non_differentiable(lse)
@@ -167,10 +168,17 @@ class _PackedTargetAttn(torch.autograd.Function):
             a.dq_raw, a.dx, a.dw = dq_raw.data_ptr(), dX.data_ptr(), dw.data_ptr()
             ws = _lib.workspace(lib.vafa_absorb_bwd_workspace_bytes(a), dev)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
-            _lib.check(lib.vafa_absorb_bwd(a, _stream()), "vafa_absorb_bwd")
-            if ctx.group is not None:
+            if ctx.group is None:
+                _lib.check(lib.vafa_absorb_bwd(a, _stream()), "vafa_absorb_bwd")
+            else:
+                # weight gradients first; their all-reduce (on the process group's own stream) then runs
+                # under the dX kernel and the dq_raw product, and the rounding below waits for it
                 import torch.distributed as dist
-                dist.all_reduce(dw, group=ctx.group)
+                _lib.check(lib.vafa_absorb_bwd_phase(a, 1, _stream()), "vafa_absorb_bwd_phase(1)")
+                work = dist.all_reduce(dw, group=ctx.group, async_op=True)
+                _lib.check(lib.vafa_absorb_bwd_phase(a, 2, _stream()), "vafa_absorb_bwd_phase(2)")
+                work.wait()
+            _lib.maybe_check_status(dev)
             if q_raw.dtype == torch.float32:
                 dwc = dw
             else:
@@ -205,6 +213,7 @@ class _TargetAttnInner(torch.autograd.Function):
             ws = _lib.workspace(lib.vafa_absorb_fwd_workspace_bytes(a), dev)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_absorb_inner_fwd(a, _stream()), "vafa_absorb_inner_fwd")
+            _lib.maybe_check_status(dev)
         ctx.save_for_backward(u, X, W_V, O, lse, cu_q, cu_k, saved)
         ctx.scale = scale
         ctx.mark_non_differentiable(lse)
@@ -233,6 +242,7 @@ class _TargetAttnInner(torch.autograd.Function):
             ws = _lib.workspace(lib.vafa_absorb_bwd_workspace_bytes(a), dev)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_absorb_inner_bwd(a, _stream()), "vafa_absorb_inner_bwd")
+            _lib.maybe_check_status(dev)
         dW_V = dw.view(d_kv, H, D_H).to(u.dtype)
         return du, dX, dW_V, None, None, None
 
@@ -249,10 +259,13 @@ def _padded_widths(dtype: torch.dtype, d_q: Optional[int], d_kv: int, H: int) ->
     return d_q_pad, 256
 
 
-def _narrow_x_ok(x_width: int, H: int, T_q: int, T_k: int) -> bool:
+def _narrow_x_ok(x_width: int, H: int, D_H: int, T_q: int, T_k: int) -> bool:
     """X (the big tensor) can stay at its own width: the forward and backward tensor-core kernels read the
-    missing columns as zero through TMA and write dX at that width (vafa_absorb_args.x_width)."""
-    return x_width % 8 == 0 and 64 % H == 0 and T_q > 0 and T_k > 0
+    missing columns as zero through TMA and write dX at that width (vafa_absorb_args.x_width).  The
+    library takes a narrow X in the backward only where its tensor-core dU / dX kernels apply
+    (H * D_H == 256, D_H >= 32, H dividing 64); every other head layout gets a padded copy of X so that
+    the backward, which then runs on the general kernels, sees full-width rows."""
+    return (x_width % 8 == 0 and H * D_H == 256 and D_H >= 32 and 64 % H == 0 and T_q > 0 and T_k > 0)
 
 
 def _pad_last(t: torch.Tensor, width: int) -> torch.Tensor:
@@ -311,7 +324,7 @@ def target_attn_inner(
     pad = _padded_widths(u.dtype, None, d_kv, H)
     if pad is not None:
         u, W_V = _pad_last(u, pad[1]), _pad_first(W_V, pad[1])
-        if not _narrow_x_ok(d_kv, H, T_q, T_k):
+        if not _narrow_x_ok(d_kv, H, D_H, T_q, T_k):
             X = _pad_last(X, pad[1])
     O, _ = _TargetAttnInner.apply(u.contiguous(), X.contiguous(), W_V.contiguous(), cu_q, cu_k, float(scale))
     return O
@@ -341,6 +354,9 @@ def packed_target_attn(
     q_raw [T_q, d_q] or [1, T_q, d_q]; X [T_k, d_kv] or [1, T_k, d_kv]; W_Q [d_q, H, D_H];
     W_K, W_V [d_kv, H, D_H].  cu_seqlens_* [n_seg+1] or *_seqinfo [n_seg] lengths.  bf16=True
     casts all five tensors to bfloat16 first.  Returns O [T_q, H, D_H] in the I/O dtype.
+
+    Device-side failures are reported through the status word, not raised by this call: see
+    `_lib.check_status` / `_lib.set_check_status` (VAFA_CHECK_STATUS=1).
     """
     _check_env_modes()
     if q_raw.dim() == 3:
@@ -375,7 +391,7 @@ def packed_target_attn(
     if pad is not None:
         q_raw, W_Q = _pad_last(q_raw, pad[0]), _pad_first(W_Q, pad[0])
         W_K, W_V = _pad_first(W_K, pad[1]), _pad_first(W_V, pad[1])
-        if not _narrow_x_ok(d_kv, H, T_q, T_k):
+        if not _narrow_x_ok(d_kv, H, D_H, T_q, T_k):
             X = _pad_last(X, pad[1])
     O, _ = _PackedTargetAttn.apply(q_raw.contiguous(), X.contiguous(), W_Q.contiguous(), W_K.contiguous(),
                                    W_V.contiguous(), cu_q, cu_k, float(scale), weight_grad_group)

@@ -14,6 +14,10 @@ namespace vafa {
 void set_error(const char* fmt, ...);
 int fail(int code, const char* fmt, ...);
 
+// Bound of every device-side wait (mbarrier spins), in units of 65536 clock cycles, as the kernels take
+// it in their launch parameters.  Set through vafa_set_wait_limit_cycles(); default about two seconds.
+int wait_limit_units();
+
 #define VAFA_CUDA_CHECK(expr)                                                              \
   do {                                                                                     \
     cudaError_t _e = (expr);                                                               \
@@ -68,6 +72,19 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+
+// The same packing for values that leave the kernel (O, dQ, dK, dV, the combine's result): IEEE
+// round-to-nearest-even and NaN stays NaN.  pack2 above is for the P / dS operands inside the block
+// loops only: its integer rounding turns a NaN whose mantissa is all ones (what the arithmetic units
+// produce) into -0, which is harmless in an operand whose row is marked NaN through its row sum, but would
+// hide a diverged run in an output.  Epilogues run once per tile, so the XU-pipe conversion costs nothing.
+template <typename T> __device__ __forceinline__ uint32_t pack2_out(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2_out<__nv_bfloat16>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <> __device__ __forceinline__ uint32_t pack2_out<__half>(float lo, float hi) { return pack2<__half>(lo, hi); }
 
 // Coalesced store of a 32-column, 16-bit chunk (64 bytes) of each lane's row.
 // In the epilogues a thread owns one row of the tile (TMEM lane = row), so a plain store of its chunk

@@ -31,6 +31,7 @@ struct GemmSmem {
   alignas(8) uint64_t b_full, a_full, a_empty, acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
 };
 static_assert(sizeof(GemmSmem) + 1024 <= 227 * 1024, "shared memory budget");
 
@@ -42,6 +43,7 @@ struct GemmParams {
   int m_tiles;     // ceil(M / 128)
   int k_chunks;    // K / 256
   int diag_heads;  // 0: full rows
+  int wait_limit;  // bound of every device-side wait, in units of 65536 cycles
 };
 
 template <typename T>
@@ -53,6 +55,7 @@ gemm_nn_k256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   volatile int* abort_flag = &sm.abort_flag;
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
     mbar_init(smem_u32(&sm.b_full), 1);
     mbar_init(smem_u32(&sm.a_full), 1);
     mbar_init(smem_u32(&sm.a_empty), 1);
@@ -158,10 +161,10 @@ gemm_nn_k256_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int v4 = 0; v4 < 4; ++v4) {
             uint4 u;
-            u.x = pack2<T>(__uint_as_float(t[8 * v4 + 0]), __uint_as_float(t[8 * v4 + 1]));
-            u.y = pack2<T>(__uint_as_float(t[8 * v4 + 2]), __uint_as_float(t[8 * v4 + 3]));
-            u.z = pack2<T>(__uint_as_float(t[8 * v4 + 4]), __uint_as_float(t[8 * v4 + 5]));
-            u.w = pack2<T>(__uint_as_float(t[8 * v4 + 6]), __uint_as_float(t[8 * v4 + 7]));
+            u.x = pack2_out<T>(__uint_as_float(t[8 * v4 + 0]), __uint_as_float(t[8 * v4 + 1]));
+            u.y = pack2_out<T>(__uint_as_float(t[8 * v4 + 2]), __uint_as_float(t[8 * v4 + 3]));
+            u.z = pack2_out<T>(__uint_as_float(t[8 * v4 + 4]), __uint_as_float(t[8 * v4 + 5]));
+            u.w = pack2_out<T>(__uint_as_float(t[8 * v4 + 6]), __uint_as_float(t[8 * v4 + 7]));
             dst[v4] = u;
           }
         }
@@ -194,6 +197,7 @@ int sm100_gemm_nn_k256(const GemmNNArgs& g, cudaStream_t s) {
       sms = 148;
   }
   GemmParams p;
+  p.wait_limit = wait_limit_units();
   p.C = g.C; p.M = g.M; p.ldc = g.ldc; p.n_tiles = g.N / kNTile; p.m_tiles = (int)((g.M + 127) / 128);
   p.diag_heads = g.diag_heads;
   p.k_chunks = g.lda / kK;

@@ -28,6 +28,7 @@ struct TnSmem {
   alignas(8) uint64_t full[kTnStages], empty[kTnStages], done;
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
 };
 static_assert(sizeof(TnSmem) + 1024 <= 227 * 1024, "shared memory budget");
 
@@ -40,6 +41,7 @@ struct TnParams {
   int n_keep;            // leading columns of the box that are kept
   int a_head_step;       // head coordinate of A for batch b: b * a_head_step
   int b_col_step;        // first B column for batch b: b * b_col_step
+  int wait_limit;        // bound of every device-side wait, in units of 65536 cycles
 };
 
 template <typename T>
@@ -51,6 +53,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   volatile int* abort_flag = &sm.abort_flag;
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
     for (int i = 0; i < kTnStages; ++i) {
       mbar_init(smem_u32(&sm.full[i]), 1);
       mbar_init(smem_u32(&sm.empty[i]), 1);
@@ -193,6 +196,7 @@ int sm100_gemm_tn(const GemmTNArgs& g, cudaStream_t s) {
     return fail(VAFA_ERR_UNSUPPORTED, "gemm_tn: n_box=%d n_keep=%d not supported", g.n_box, g.n_keep);
   const int sms = g.sm_count > 0 ? g.sm_count : 148;
   TnParams p;
+  p.wait_limit = wait_limit_units();
   p.partial = (float*)g.workspace;
   p.n_chunks = (int)((g.T + kChunk - 1) / kChunk);
   p.splits = tn_splits(g.T, g.batch, sms);

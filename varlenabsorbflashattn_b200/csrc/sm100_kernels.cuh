@@ -29,6 +29,10 @@ struct Bwd128Launch {
 };
 int sm100_varlen_bwd128_launch(const Bwd128Launch& L, cudaStream_t s);
 
+// One CTA waits, with the bounded wait every kernel uses, on an mbarrier that nobody arrives on; when the
+// wait runs out it reports code 1 / site 900 through the status word and returns.
+int sm100_selftest_bounded_wait(int32_t* status, cudaStream_t s);
+
 // ---- absorb operator on the tcgen05 kernels ------------------------------------------------
 // Attention core on a pre-projected u: axn[t,h,:] = softmax_h(scale * u[t,h,:] . X^T) . X, normalised,
 // in the I/O dtype; lse[t,h] log2-domain.  Requires d_kv == 256, 16-bit dtype, H dividing 128.
@@ -63,6 +67,7 @@ struct AbsorbCoreBwdArgs {
   int32_t* status;
   int x_width;         // row width of x and dx (<= 256)
   int lists_built;     // the tile lists were already built by sm100_absorb_core_bwd_lists()
+  int which;           // 0: both kernels; 1: the dU kernel only; 2: the dX kernel only
 };
 size_t sm100_absorb_core_bwd_workspace_bytes(int total_q, int total_k, int n_seg, int H);
 int sm100_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s);

@@ -44,17 +44,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role sets when it gives up, so that
 // the other roles leave their waits promptly.  Returns false when the wait did not complete.
-constexpr long long kWaitLimitCycles = 4000000000LL;  // about two seconds at 2 GHz
+// The word after it (abort_flag[1]) holds the limit in units of 65536 clock cycles; the kernel copies it
+// there from its launch parameters (host side: wait_limit_units(), set by vafa_set_wait_limit_cycles).
+constexpr long long kDefaultWaitLimitCycles = 4000000000LL;  // about two seconds at 2 GHz
+__device__ __forceinline__ long long wait_limit_cycles(volatile int* abort_flag) {
+  return (long long)abort_flag[1] << 16;
+}
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = wait_limit_cycles(abort_flag);
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         return false;
       }
@@ -67,13 +73,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ int mbar_wait_either(uint32_t bar_a, uint32_t parity_a, uint32_t bar_b, uint32_t parity_b,
                                                 volatile int* abort_flag) {
   const long long t0 = clock64();
+  const long long limit = wait_limit_cycles(abort_flag);
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar_a, parity_a)) return 1;
     if (mbar_try_wait(bar_b, parity_b)) return 2;
     if ((++spins & 63u) == 0u) {
       if (*abort_flag != 0) return 0;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         return 0;
       }

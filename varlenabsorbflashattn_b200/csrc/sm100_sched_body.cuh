@@ -132,6 +132,7 @@ __device__ __forceinline__ void for_each_segment(const SchedParams& p, int G, F 
 __device__ __forceinline__ void sched_build(const SchedParams& p) {
   __shared__ int s_hist[kBuckets];
   __shared__ int s_units, s_items, s_rows, s_bs, s_combine;
+  __shared__ unsigned long long s_items64, s_rows64;  // pass 2 counts in 64 bits
   __shared__ long long s_blocks;
 
   if (threadIdx.x == 0) { s_units = 0; s_blocks = 0; s_combine = 0; }
@@ -195,24 +196,27 @@ __device__ __forceinline__ void sched_build(const SchedParams& p) {
   }
   // pass 2: make the split fit the capacities (double the slice until it does)
   for (int round = 0; any_split && round < 24; ++round) {
-    if (threadIdx.x == 0) { s_items = 0; s_rows = 0; }
+    if (threadIdx.x == 0) { s_items64 = 0; s_rows64 = 0; }
     __syncthreads();
     const int bs = s_bs;
-    int items = 0, rows = 0;
+    // counted in 64 bits: a short forced slice on very long sequences can pass 2^31 partial rows, and a
+    // wrapped 32-bit sum would pass the capacity test below
+    long long items = 0, rows = 0;
     for_each_segment(p, G, [&](const Seg& g, int t0, int ts) {
       for (int t = t0; t < g.n_tiles; t += ts) {
         const Unit u = make_unit(p, g, t);
         const int ns = n_splits(n_blocks(u.i_len), bs);
         items += ns;
-        if (ns > 1) rows += ns * u.o_rows;
+        if (ns > 1) rows += (long long)ns * u.o_rows;
       }
     });
-    items = (int)warp_sum_ll(items);
-    rows = (int)warp_sum_ll(rows);
-    if (lane == 0 && items) atomicAdd(&s_items, items);
-    if (lane == 0 && rows) atomicAdd(&s_rows, rows);
+    items = warp_sum_ll(items);
+    rows = warp_sum_ll(rows);
+    if (lane == 0 && items) atomicAdd(&s_items64, (unsigned long long)items);
+    if (lane == 0 && rows) atomicAdd(&s_rows64, (unsigned long long)rows);
     __syncthreads();
-    const bool fits = ((long long)s_items * p.H <= p.cap_items) && (s_rows <= p.cap_rows);
+    const bool fits = (s_items64 <= (unsigned long long)p.cap_items / (unsigned long long)p.H) &&
+                      (s_rows64 <= (unsigned long long)max(p.cap_rows, 0));
     __syncthreads();
     if (fits || s_bs == 0) break;
     if (threadIdx.x == 0) s_bs = (s_bs >= (1 << 24)) ? 0 : s_bs * 2;

@@ -86,6 +86,7 @@ struct BwdSmem {
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
 };
 
 static_assert(sizeof(BwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(BwdSmem<64>) + 1024 <= 227 * 1024 &&
@@ -103,6 +104,7 @@ struct BwdParams {
   float scale;
   float scale_log2;
   int32_t* status;
+  int wait_limit;        // bound of every device-side wait, in units of 65536 cycles
   int out_width;         // absorb dX: columns written per row (= row stride of the output), <= D
   long long* trace;
 };
@@ -132,6 +134,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
     wq_init(sm.wq, 9);
     mbar_init(smem_u32(&sm.outer_full), 1);
     mbar_init(smem_u32(&sm.outer_free), 1);
@@ -390,7 +393,7 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
           }
           uint32_t pw[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
+          for (int i = 0; i < 16; ++i) pw[i] = pack2_out<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
           // consecutive tile rows are consecutive output rows in every mode of this template
           const long long row_stride = kAbsorb ? (long long)out_w : (long long)p.H * D;
           const int n_valid_rows = (kAbsorb && !kDKV) ? w.o_rows * p.H : w.o_rows;
@@ -906,6 +909,7 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   if ((rc = encode_tmap_rows(&g64, a.dax, a.dtype, a.total_q, a.H, D, kInner / a.H, a.H))) return rc;
 
   BwdParams p;
+  p.wait_limit = wait_limit_units();
   p.ld = (const float2*)a.ld; p.ld_stride = sm100_absorb_ld_pad((long long)a.total_q * a.H); p.H = a.H; p.scale = a.scale; p.scale_log2 = a.scale * kLog2e; p.status = a.status;
   p.out_width = a.x_width;
   p.trace = nullptr;
@@ -919,7 +923,7 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
   }
 #endif
   p.out1 = nullptr;
-  {
+  if (a.which != 2) {
     p.out0 = a.du; p.header = sq.header; p.items = sq.items;
     const size_t smem = sizeof(BwdSmem<D, false, true>) + 1024;
     VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -927,7 +931,7 @@ int launch_absorb_core_bwd(const AbsorbCoreBwdArgs& a, cudaStream_t s) {
     varlen_bwd_kernel<T, D, false, true><<<sms, kBwdThreads, smem, s>>>(u128, g128, x64, x64, p);
   }
   VAFA_LAUNCH_CHECK("varlen_bwd_kernel<absorb dU>");
-  {
+  if (a.which != 1) {
     p.out0 = a.dx; p.header = sk.header; p.items = sk.items;
     const size_t smem = sizeof(BwdSmem<D, true, true>) + 1024;
     VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd_kernel<T, D, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

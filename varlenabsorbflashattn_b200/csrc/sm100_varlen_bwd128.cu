@@ -82,6 +82,7 @@ struct Smem128 {
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
 };
 static_assert(sizeof(Smem128<128, false>) + 1024 <= 227 * 1024 && sizeof(Smem128<128, true>) + 1024 <= 227 * 1024 &&
                   sizeof(Smem128<64, false>) + 1024 <= 227 * 1024 && sizeof(Smem128<64, true>) + 1024 <= 227 * 1024,
@@ -98,6 +99,7 @@ struct Params128 {
   float scale;
   float scale_log2;
   int32_t* status;
+  int wait_limit;    // bound of every device-side wait, in units of 65536 cycles
   long long* trace;
 };
 
@@ -119,6 +121,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
     wq_init(sm.wq, 9);
     mbar_init(smem_u32(&sm.outer_full), 1);
     mbar_init(smem_u32(&sm.outer_free), 1);
@@ -465,7 +468,10 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         T* optr = reinterpret_cast<T*>(which == 0 ? p.out0 : p.out1) + out_row * D;
         // dV unscaled; dQ and dK scaled; dQ rows that saw no key are exact zeros (the polynomial 2^t
         // leaves about 1e-38 where the special-function unit gives 0)
-        const float mul = (kDKV && which == 0) ? 1.f : ((!kDKV && neg_lse == -INFINITY) ? 0.f : p.scale);
+        // a row whose lse or delta is NaN (the forward saw a NaN, or dO holds one) goes out as NaN: the packed
+        // dS operand cannot carry it (see pack2)
+        const float poison = kDKV ? 0.f : ((neg_lse == -INFINITY ? 0.f : neg_lse * 0.f) + my_delta * 0.f);
+        const float mul = (kDKV && which == 0) ? 1.f : ((!kDKV && neg_lse == -INFINITY) ? 0.f : p.scale + poison);
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
 #pragma unroll
         for (int c2 = 0; c2 < D / 64; ++c2) {
@@ -480,7 +486,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
           }
           uint32_t pw[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
+          for (int i = 0; i < 16; ++i) pw[i] = pack2_out<T>(__uint_as_float(t[2 * i]) * mul, __uint_as_float(t[2 * i + 1]) * mul);
           store_chunk_coalesced<T>(pw, optr + cc * 32, (long long)p.H * D, r, w.o_rows, 4);
         }
       }
@@ -515,6 +521,7 @@ long long* vafa_trace_buffer_bwd = nullptr;
 template <typename T, int D>
 static int launch128(const Bwd128Launch& L, cudaStream_t s) {
   Params128 p;
+  p.wait_limit = wait_limit_units();
   p.ld = (const float2*)L.ld; p.ld_stride = L.ld_stride; p.H = L.H;
   p.scale = L.scale; p.scale_log2 = L.scale * kLog2e; p.status = L.status;
   p.trace = nullptr;

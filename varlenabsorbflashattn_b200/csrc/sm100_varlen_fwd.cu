@@ -82,6 +82,7 @@ struct FwdSmem {
   WorkQueue wq;
   uint32_t tmem_base;
   int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
 };
 
 static_assert(sizeof(FwdSmem<128>) + 1024 <= 227 * 1024 && sizeof(FwdSmem<64>) + 1024 <= 227 * 1024 &&
@@ -98,6 +99,7 @@ struct FwdParams {
   int H;
   float scale_log2;
   int32_t* status;
+  int wait_limit;  // bound of every device-side wait, in units of 65536 cycles
   long long* trace;
 };
 
@@ -123,6 +125,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
 
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
     wq_init(sm.wq, 9);
     for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&sm.pair_bar[i]), 64);
     mbar_init(smem_u32(&sm.q_full), 1);
@@ -459,7 +462,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         ++pair_cnt;
         l_tot = l + sm.xsum[half ^ 1][r];
       }
-      const bool dead = (nb == 0) || !(l_tot > 0.f);
+      const bool dead = (nb == 0) || (l_tot == 0.f);  // a NaN row sum is not a dead row: it goes out as NaN
       const float inv_l = dead ? 0.f : 1.f / l_tot;
       const float lse_val = dead ? -INFINITY : m_ref + log2f(l_tot);
       if (w.partial < 0) {
@@ -479,7 +482,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
           uint32_t pw[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            pw[i] = pack2<T>(__uint_as_float(t[2 * i]) * inv_l, __uint_as_float(t[2 * i + 1]) * inv_l);
+            pw[i] = pack2_out<T>(__uint_as_float(t[2 * i]) * inv_l, __uint_as_float(t[2 * i + 1]) * inv_l);
           // rows of the tile are consecutive (token, head) rows of O: H*D apart (absorb: D apart)
           store_chunk_coalesced<T>(pw, optr + cc * 32, kAbsorb ? (long long)D : (long long)p.H * D, r,
                                    kAbsorb ? w.o_rows * p.H : w.o_rows, 4);
@@ -580,18 +583,18 @@ __global__ void __launch_bounds__(256) varlen_combine_kernel(const SchedHeader* 
           acc[0] += wgt * f.x; acc[1] += wgt * f.y;
         }
       }
-      const float inv = den > 0.f ? 1.f / den : 0.f;
+      const float inv = den == 0.f ? 0.f : 1.f / den;  // a NaN weight sum goes out as NaN
       const long long row = (long long)cu.q_start + r;
       T* dst = o + (row * H + h) * D + lane * V;
       if (V == 4) {
         uint2 pk;
-        pk.x = pack2<T>(acc[0] * inv, acc[1] * inv);
-        pk.y = pack2<T>(acc[V - 2] * inv, acc[V - 1] * inv);
+        pk.x = pack2_out<T>(acc[0] * inv, acc[1] * inv);
+        pk.y = pack2_out<T>(acc[V - 2] * inv, acc[V - 1] * inv);
         *reinterpret_cast<uint2*>(dst) = pk;
       } else {
-        *reinterpret_cast<uint32_t*>(dst) = pack2<T>(acc[0] * inv, acc[1] * inv);
+        *reinterpret_cast<uint32_t*>(dst) = pack2_out<T>(acc[0] * inv, acc[1] * inv);
       }
-      if (lane == 0) lse[row * H + h] = den > 0.f ? m_use + log2f(den) : -INFINITY;
+      if (lane == 0) lse[row * H + h] = den == 0.f ? -INFINITY : m_use + log2f(den);
     }
   }
 }
@@ -658,6 +661,7 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   if ((rc = encode_tmap_rows(&tv, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
 
   FwdParams p;
+  p.wait_limit = wait_limit_units();
   p.o = a->o; p.lse = a->lse;
   p.partial_lse = (float*)(base + ws.plse);
   p.partial_o = (float*)(base + ws.po);
@@ -730,6 +734,7 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   if ((rc = encode_tmap_rows(&tu, a.u, a.dtype, a.total_q, a.H, D, kTile / a.H, a.H))) return rc;
   if ((rc = encode_tmap_rows(&tx, a.x, a.dtype, a.total_k, 1, a.x_width, fwd_block_keys<true>()))) return rc;
   FwdParams p;
+  p.wait_limit = wait_limit_units();
   p.o = a.axn; p.lse = a.lse; p.partial_o = nullptr; p.partial_lse = nullptr;
   p.header = sp.header; p.items = sp.items; p.H = a.H;
   p.scale_log2 = a.scale * kLog2e;

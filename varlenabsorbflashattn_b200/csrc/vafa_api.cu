@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -25,6 +26,13 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
   return code;
+}
+
+static std::atomic<long long> g_wait_limit_cycles{4000000000LL};  // about two seconds at 2 GHz
+
+int wait_limit_units() {
+  const long long u = (g_wait_limit_cycles.load(std::memory_order_relaxed) + 65535) >> 16;
+  return (int)(u < 1 ? 1 : (u > 0x7fffffffLL ? 0x7fffffffLL : u));
 }
 
 namespace {
@@ -231,7 +239,7 @@ size_t absorb_fwd_ws_bytes(const vafa_absorb_args* a, bool inner) {
   return n;
 }
 
-int absorb_fwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
+int absorb_forward(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   const AbsorbSizes z = absorb_sizes(a);
   const AbsorbFast fast = absorb_fast(a, inner);
   char* sv = (char*)a->saved;
@@ -326,7 +334,10 @@ bool absorb_bwd_core_fast(const vafa_absorb_args* a, bool inner) {
   return f.core && f.epilogue && (64 % a->num_heads) == 0 && al(a->d_o) && al(a->dx) && al(a->dq_raw);
 }
 
-int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
+// phase: 0 = the whole backward; 1 = everything the weight gradients need (and du); 2 = the rest (dX and
+// dq_raw), reading what phase 1 left in the workspace.  Only the tensor-core chain can be cut: on the
+// other paths phase 1 is the whole backward and phase 2 nothing.
+int absorb_backward(const vafa_absorb_args* a, bool inner, int phase, cudaStream_t s) {
   const AbsorbSizes z = absorb_sizes(a);
   char* sv = (char*)a->saved;
   char* ws = (char*)a->workspace;
@@ -345,10 +356,26 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
   // weight-gradient chain on the tensor-core GEMMs: needs the dU/dX fast path's preconditions, D_H = 32
   // (the 64-column box trick of the token reductions) and, for the full operator, d_q = 256
   const bool fast_chain = absorb_bwd_core_fast(a, inner) && dh == 32 && (inner || (dq >= 256 && dq % 256 == 0));
+  const bool cut = fast_chain && !inner && phase != 0;
+  if (phase == 2 && !cut) return 0;
   // tile lists of the dU and dX kernels: built on the side stream beside the products below
   SideGuard side(s);
   AbsorbCoreBwdArgs cb{u, a->x, dax, nullptr, du, a->dx, a->cu_seqlens_q, a->cu_seqlens_k, a->n_seg, Tq, a->total_k, H,
-                       a->dtype, a->scale, a->sm_count, nullptr, a->status, x_width_of(a), 0};
+                       a->dtype, a->scale, a->sm_count, nullptr, a->status, x_width_of(a), 0, 0};
+  if (cut && phase == 2) {
+    // the tile lists, the (lse, delta) rows, dax, du and dp are where phase 1 left them
+    const AbsorbBwdExtra x = absorb_bwd_extra(a);
+    char* ex = ws + z.dax + z.delta + z.du + z.dp;
+    cb.workspace = ex + x.ld + x.bexp;
+    cb.ld = ex;
+    cb.lists_built = 1;
+    cb.which = 2;
+    if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
+    void* wqt = ex + x.ld + x.bexp + x.sched + x.tn;
+    if ((rc = sm100_transpose(a->w_q, wqt, dq, H * dh, a->dtype, s))) return rc;
+    GemmNNArgs gq{dp, wqt, a->dq_raw, Tq, dq, H * dh, dq, dq, a->dtype, 0, a->sm_count};
+    return sm100_gemm_nn_k256(gq, s);
+  }
   if (absorb_bwd_core_fast(a, inner)) {
     const AbsorbBwdExtra x = absorb_bwd_extra(a);
     cb.workspace = ws + z.dax + z.delta + z.du + z.dp + x.ld + x.bexp;
@@ -380,6 +407,7 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     if ((rc = sm100_gemm_nn_k256(gd, s))) return rc;
     if ((rc = sm100_absorb_ld(a->o, a->d_o, a->lse, ld, (long long)Tq * H, dh, a->scale, a->dtype, s))) return rc;
     cb.ld = ld;
+    cb.which = cut ? 1 : 0;
     if ((rc = side.join())) return rc;
     if ((rc = sm100_absorb_core_bwd(cb, s))) return rc;
   } else {
@@ -414,6 +442,7 @@ int absorb_bwd_simt(const vafa_absorb_args* a, bool inner, cudaStream_t s) {
     GemmTNArgs tq{a->q_raw, dp, dWQ, tn_ws, Tq, a->dtype, q_chunks, q_chunks, 256, 256, H * dh, 0,
                   (long long)256 * H * dh, (long long)H * dh, a->sm_count};
     if ((rc = sm100_gemm_tn(tq, s))) return rc;
+    if (cut) return 0;  // phase 1 ends with the last weight gradient
     // dq_raw = dp W_Q^T   (W_Q is [d_q, H*D_H]; its transpose [H*D_H, d_q])
     if ((rc = sm100_transpose(a->w_q, wqt, dq, H * dh, a->dtype, s))) return rc;
     GemmNNArgs gq{dp, wqt, a->dq_raw, Tq, dq, H * dh, dq, dq, a->dtype, 0, a->sm_count};
@@ -535,7 +564,7 @@ int vafa_absorb_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   const int impl = pick_impl(a->impl, absorb_fast(a, false).core, "absorb_fwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, false)))) return rc;
-  return absorb_fwd_simt(a, false, (cudaStream_t)stream);
+  return absorb_forward(a, false, (cudaStream_t)stream);
 }
 int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, false);
@@ -544,7 +573,17 @@ int vafa_absorb_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
-  return absorb_bwd_simt(a, false, (cudaStream_t)stream);
+  return absorb_backward(a, false, 0, (cudaStream_t)stream);
+}
+int vafa_absorb_bwd_phase(const vafa_absorb_args* a, int32_t phase, vafa_stream_t stream) {
+  if (phase < 0 || phase > 2) return fail(VAFA_ERR_INVALID, "bad phase %d", phase);
+  int rc = check_absorb(a, true, false);
+  if (rc) return rc;
+  if ((rc = check_x_width(a, absorb_bwd_core_fast(a, false)))) return rc;
+  const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_bwd");
+  if (impl < 0) return impl;
+  if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
+  return absorb_backward(a, false, phase, (cudaStream_t)stream);
 }
 int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, false, true);
@@ -553,7 +592,7 @@ int vafa_absorb_inner_fwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   const int impl = pick_impl(a->impl, absorb_fast(a, true).core, "absorb_inner_fwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, absorb_fwd_ws_bytes(a, true)))) return rc;
-  return absorb_fwd_simt(a, true, (cudaStream_t)stream);
+  return absorb_forward(a, true, (cudaStream_t)stream);
 }
 int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   int rc = check_absorb(a, true, true);
@@ -562,12 +601,23 @@ int vafa_absorb_inner_bwd(const vafa_absorb_args* a, vafa_stream_t stream) {
   const int impl = pick_impl(a->impl == VAFA_IMPL_TCGEN05 ? VAFA_IMPL_AUTO : a->impl, false, "absorb_inner_bwd");
   if (impl < 0) return impl;
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_absorb_bwd_workspace_bytes(a)))) return rc;
-  return absorb_bwd_simt(a, true, (cudaStream_t)stream);
+  return absorb_backward(a, true, 0, (cudaStream_t)stream);
 }
 
 int vafa_cast_from_f32(const float* src, void* dst, size_t n, int32_t dtype, vafa_stream_t stream) {
   if (n > 0 && (!src || !dst)) return fail(VAFA_ERR_INVALID, "null pointer");
   return cast_from_f32(src, dst, n, dtype, (cudaStream_t)stream);
+}
+
+long long vafa_set_wait_limit_cycles(long long cycles) {
+  const long long prev = g_wait_limit_cycles.load(std::memory_order_relaxed);
+  if (cycles > 0) g_wait_limit_cycles.store(cycles, std::memory_order_relaxed);
+  return prev;
+}
+
+int vafa_selftest_bounded_wait(int32_t* status, vafa_stream_t stream) {
+  if (!status) return fail(VAFA_ERR_INVALID, "null status word");
+  return sm100_selftest_bounded_wait(status, (cudaStream_t)stream);
 }
 
 int vafa_check_status(const int32_t* status, vafa_stream_t stream) {

@@ -136,6 +136,7 @@ class _PackedVarlenAttn(torch.autograd.Function):
             ws = _lib.workspace(lib.vafa_varlen_fwd_workspace_bytes(a), q.device)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_varlen_fwd(a, torch.cuda.current_stream().cuda_stream), "vafa_varlen_fwd")
+            _lib.maybe_check_status(q.device)
         ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k)
         ctx.scale, ctx.causal, ctx.split_k_block = scale, causal, split_k_block
         ctx.mark_non_differentiable(lse)
@@ -156,6 +157,7 @@ class _PackedVarlenAttn(torch.autograd.Function):
             ws = _lib.workspace(lib.vafa_varlen_bwd_workspace_bytes(a), q.device)
             a.workspace, a.workspace_bytes = _lib.ptr(ws), 0 if ws is None else ws.numel()
             _lib.check(lib.vafa_varlen_bwd(a, torch.cuda.current_stream().cuda_stream), "vafa_varlen_bwd")
+            _lib.maybe_check_status(q.device)
         return dq, dk, dv, None, None, None, None, None
 
 
@@ -202,6 +204,11 @@ def packed_varlen_attn(
 
     Returns o with the layout of q.  A query row that sees no key (empty KV segment, or masked
     out entirely) yields zeros.
+
+    Failures found on the device (a wait inside a kernel that ran out, a tile list that outgrew its
+    buffer) do not raise here: the call only enqueues work.  They are written to a per-device status
+    word; `_lib.check_status(device)` reads it (it synchronises), and `_lib.set_check_status(True)` or
+    VAFA_CHECK_STATUS=1 makes every call do so.
     """
     q3, k3, v3, cu_q, cu_k, scale, was4 = _prepare(q, k, v, cu_seqlens_q, cu_seqlens_k, q_seqinfo, k_seqinfo, scale)
     o, _ = _PackedVarlenAttn.apply(q3, k3, v3, cu_q, cu_k, scale, bool(causal), split_k_block)
