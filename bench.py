@@ -23,7 +23,7 @@ own oracle on a bounded sample, N=1 only), `vs_reference_gpu` (N=1 only: the ref
 and flash-attn timed in a child process on the same GPU and the same seeded inputs, on the shapes their
 32-bit indexing can address) and the GPU clocks sampled during the timed regions.
 
-Other workloads: C2, C2b, S1 (named length generators), `stage1:<row>` (a row of the reference's logged
+Other workloads: C5s (the leading 1/16 of C5, for profiler captures), C2, C2b, S1 (named length generators), `stage1:<row>` (a row of the reference's logged
 production shapes, tests/golden/stage1_shapes.jsonl.gz) for the varlen operator, and `absorb-prod:<i>`
 (record i of tests/golden/real_shape_all.json.gz; d_q=968, d_kv=216) / `C4` for the absorb operator
 alone.
@@ -171,6 +171,16 @@ def workload(name: str) -> dict:
         c = CONFIGS["C5v"]
         return dict(kind="varlen", name="C5", ql=ql, kl=kl, H=c["H"], D=c["D"], causal=c["causal"], absorb="C5a",
                     label="C5: one packed batch, lengths logU[128,8192] seed 0, causal")
+    if name == "C5s":
+        # the leading sequences of C5 that hold 1/16 of its tokens: the same kernels and head count on a few GB,
+        # small enough for a profiler capture
+        ql, _ = config_lengths("C5v", 0)
+        n, acc = 0, 0
+        while acc + ql[n] <= 62_500:
+            acc += ql[n]; n += 1
+        c = CONFIGS["C5v"]
+        return dict(kind="varlen", name="C5s", ql=ql[:n], kl=ql[:n], H=c["H"], D=c["D"], causal=c["causal"], absorb=None,
+                    label=f"C5s: the first {n} sequences of C5")
     if name in ("C2", "C2b", "S1", "C3"):
         ql, kl = config_lengths(name, 0)
         c = CONFIGS[name]

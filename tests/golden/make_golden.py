@@ -16,8 +16,11 @@ import math
 import os
 import sys
 
-os.environ.setdefault("TRITON_INTERPRET", "1")
-sys.dont_write_bytecode = True
+if __name__ == "__main__":
+    # only when generating: the tests import this module for its case tables, in a process that may
+    # also run the reference's kernels on a GPU, where the interpreter must stay off
+    os.environ.setdefault("TRITON_INTERPRET", "1")
+    sys.dont_write_bytecode = True
 
 import numpy as np
 import torch

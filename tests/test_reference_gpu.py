@@ -40,6 +40,8 @@ def _ref_pkgs():
         pytest.skip("baseline/_ref is absent (bash baseline/install_ref.sh)")
     if REF_DIR not in sys.path:
         sys.path.insert(0, REF_DIR)
+    # the reference must be compiled for the GPU here, not run by Triton's CPU interpreter
+    assert os.environ.get("TRITON_INTERPRET", "0") in ("", "0"), "TRITON_INTERPRET is set in this process"
     import triton_fa_varlen_v2 as R
     import triton_target_attn_absorb as RA
     return R, RA
@@ -58,6 +60,7 @@ def _errs(got, ref):
 
 
 def _no_worse(name, ours, theirs, who):
+    assert theirs["rel_l2"] < 0.1, f"{name}: {who} itself is off by rel-L2 {theirs['rel_l2']:.3e}: the comparison is void"
     bound = max(2.0 * theirs["rel_l2"], 1.5 * ours["floor"], 1e-3)
     assert ours["rel_l2"] <= bound, f"{name}: rel-L2 {ours['rel_l2']:.3e} vs {who} {theirs['rel_l2']:.3e} (floor {ours['floor']:.3e})"
     bound_abs = max(2.0 * theirs["max_abs"], 2e-2)
