@@ -5,7 +5,7 @@ folder is not part of the repository's history, so these tests skip where it is 
 runs three implementations on the same device tensors -- this library, the reference's Triton
 kernels through their public API, and flash-attn's `flash_attn_varlen_func` -- and holds all of
 them to the fp32 CPU oracle.  The assertion is the second half of the parity criterion: this
-library's error is no worse than the reference's on the same inputs (within a factor of 2, or
+library's error is no worse than the reference's on the same inputs (within a factor of 1.3 in rel-L2 and 1.5 in max-abs, or
 within 1.5x of the error that rounding the exact result to bf16 causes, whichever is larger), for
 O, the LSE and every gradient.
 
@@ -61,9 +61,9 @@ def _errs(got, ref):
 
 def _no_worse(name, ours, theirs, who):
     assert theirs["rel_l2"] < 0.1, f"{name}: {who} itself is off by rel-L2 {theirs['rel_l2']:.3e}: the comparison is void"
-    bound = max(2.0 * theirs["rel_l2"], 1.5 * ours["floor"], 1e-3)
+    bound = max(1.3 * theirs["rel_l2"], 1.5 * ours["floor"], 1e-3)
     assert ours["rel_l2"] <= bound, f"{name}: rel-L2 {ours['rel_l2']:.3e} vs {who} {theirs['rel_l2']:.3e} (floor {ours['floor']:.3e})"
-    bound_abs = max(2.0 * theirs["max_abs"], 2e-2)
+    bound_abs = max(1.5 * theirs["max_abs"], 2e-2)
     assert ours["max_abs"] <= bound_abs, f"{name}: max-abs {ours['max_abs']:.3e} vs {who} {theirs['max_abs']:.3e}"
 
 
