@@ -95,6 +95,20 @@ size_t vafa_varlen_bwd_workspace_bytes(const vafa_varlen_args* a);
 int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream);
 int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream);
 
+/* Which backward vafa_varlen_bwd runs on the tensor-core path (process-wide; returns the previous mode;
+ * other values only read it):
+ *   0  the dQ kernel and the dK/dV kernel (the reference's own split,
+ *      triton_fa_varlen_v2/triton_fa_varlen_v2/interface.py:283-338): seven matrix products per score
+ *      tile, no atomics, dQ/dK/dV bit-identical from run to run like the reference's
+ *      (triton_fa_varlen_v2/triton_fa_varlen_v2/test_smoke.py:496-531).  The default.
+ *   1  one pass over the score tiles for head_dim 128 (five products, one exponential per score; the
+ *      reference's authors sketched this as _bwd_fused_kernel, kernels.py:923-1099, and never launched
+ *      it): dK and dV as before, dQ summed across key tiles by fp32 reductions in global memory, so its
+ *      last bits depend on the order in which the tiles finish.  Other head dims run mode 0.
+ * vafa_varlen_bwd_workspace_bytes() depends on the mode (mode 1 adds an fp32 [T_q, H, D] array): query
+ * it after setting the mode. */
+int vafa_set_varlen_bwd_mode(int mode);
+
 /* Forward pass for callers that cannot provide a workspace.  No counterpart in the reference:
  * there, torch's allocator is always at hand.  Some hosts of this library are not in that
  * position -- a plugin running inside another runtime's execution callback, an inference engine

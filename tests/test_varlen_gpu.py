@@ -316,3 +316,36 @@ def test_status_check_after_every_call_is_opt_in():
         _compare(ins, o, lse, grads, torch.bfloat16, False)
     finally:
         _lib.set_check_status(False)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("name", ["cross_block", "stage1_like", "stage2_like", "empty_q_and_k", "ones", "long"])
+def test_fused_backward_mode(name, causal):
+    """The one-pass backward (opt-in, head dim 128): same tolerances against the oracle as the default kernel
+    pair; dK and dV are bit-identical to the pair's (same products in the same order), dQ is summed across
+    key tiles in global memory and agrees to rounding."""
+    ql, kl = CASES[name] if name in CASES else ([700, 45, 1300], [1500, 45, 1300])
+    V.set_impl("tcgen05")
+    try:
+        vb.set_backward_mode("split")
+        ins, o, lse, gs = _run(ql, kl, 2, 128, torch.bfloat16, causal, seed=3)
+        assert vb.set_backward_mode("fused") == "split"
+        _, o2, _, gf = _run(ql, kl, 2, 128, torch.bfloat16, causal, seed=3)
+    finally:
+        vb.set_backward_mode("split")
+        V.set_impl("auto")
+    _compare(ins, o2, lse, gf, torch.bfloat16, causal)
+    assert torch.equal(gs[1], gf[1]) and torch.equal(gs[2], gf[2])
+    ref = float(gs[0].float().abs().max())
+    assert float((gs[0].float() - gf[0].float()).abs().max()) <= 2e-2 * max(1.0, ref)
+
+
+def test_fused_backward_mode_leaves_other_head_dims_to_the_kernel_pair():
+    V.set_impl("tcgen05")
+    try:
+        vb.set_backward_mode("fused")
+        ins, o, lse, grads = _run([200, 64], [200, 300], 2, 64, torch.float16, True)
+    finally:
+        vb.set_backward_mode("split")
+        V.set_impl("auto")
+    _compare(ins, o, lse, grads, torch.float16, True)

@@ -28,7 +28,7 @@ EXPORTS = (
     "vafa_absorb_saved_bytes", "vafa_absorb_fwd_workspace_bytes", "vafa_absorb_bwd_workspace_bytes",
     "vafa_absorb_fwd", "vafa_absorb_bwd", "vafa_absorb_bwd_phase", "vafa_absorb_inner_fwd", "vafa_absorb_inner_bwd",
     "vafa_profile_enable", "vafa_profile_kernel_count", "vafa_profile_kernel_name", "vafa_profile_read",
-    "vafa_profile_reset", "vafa_set_wait_limit_cycles", "vafa_selftest_bounded_wait",
+    "vafa_profile_reset", "vafa_set_wait_limit_cycles", "vafa_selftest_bounded_wait", "vafa_set_varlen_bwd_mode",
 )
 
 
@@ -95,6 +95,8 @@ def load() -> C.CDLL:
             getattr(lib, name).restype = C.c_int
         lib.vafa_absorb_bwd_phase.argtypes = [C.POINTER(AbsorbArgs), C.c_int32, C.c_void_p]
         lib.vafa_absorb_bwd_phase.restype = C.c_int
+        lib.vafa_set_varlen_bwd_mode.argtypes = [C.c_int]
+        lib.vafa_set_varlen_bwd_mode.restype = C.c_int
         lib.vafa_set_wait_limit_cycles.argtypes = [C.c_longlong]
         lib.vafa_set_wait_limit_cycles.restype = C.c_longlong
         lib.vafa_selftest_bounded_wait.argtypes = [C.c_void_p, C.c_void_p]

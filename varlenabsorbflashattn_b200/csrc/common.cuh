@@ -18,6 +18,10 @@ int fail(int code, const char* fmt, ...);
 // it in their launch parameters.  Set through vafa_set_wait_limit_cycles(); default about two seconds.
 int wait_limit_units();
 
+// Which backward packed_varlen_attn runs on the tcgen05 path: 0 = the dQ + dK/dV kernel pair (bit-reproducible
+// gradients, the default), 1 = the one-pass kernel where it applies (head dim 128).  vafa_set_varlen_bwd_mode().
+int varlen_bwd_mode();
+
 #define VAFA_CUDA_CHECK(expr)                                                              \
   do {                                                                                     \
     cudaError_t _e = (expr);                                                               \

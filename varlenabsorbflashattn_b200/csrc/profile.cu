@@ -13,7 +13,8 @@ namespace {
 const char* kNames[kKCount] = {
     "sched_kernel", "varlen_fwd_kernel", "varlen_combine_kernel", "bwd_preprocess_kernel", "varlen_bwd_kernel<dQ>",
     "varlen_bwd_kernel<dKV>", "simt_fwd_kernel", "simt_delta_kernel", "simt_dq_kernel", "simt_dkv_kernel",
-    "simt_gemm_kernel", "cast_kernel", "varlen_fwd_kernel<absorb>", "varlen_bwd_kernel<absorb dU>", "gemm_nn_k256_kernel", "varlen_bwd_kernel<absorb dX>", "gemm_tn_kernel"};
+    "simt_gemm_kernel", "cast_kernel", "varlen_fwd_kernel<absorb>", "varlen_bwd_kernel<absorb dU>", "gemm_nn_k256_kernel", "varlen_bwd_kernel<absorb dX>", "gemm_tn_kernel",
+    "varlen_bwd_kernel<fused>", "dq_finalize_kernel"};
 
 std::atomic<long long> g_launches[kKCount];
 std::atomic<int> g_enabled{0};

@@ -23,6 +23,8 @@ enum KernelId {
   kKAbsorbGemm,
   kKAbsorbBwdDx,
   kKAbsorbGemmTn,
+  kKBwdFused,
+  kKBwdDqFin,
   kKCount
 };
 

@@ -26,8 +26,12 @@ struct Bwd128Launch {
   float scale;
   int32_t* status;
   int run_dq, run_dkv;  // which of the two kernels to launch
+  float* dq_acc;        // fused backward only: fp32 [T_q, H, D] accumulator of dQ
 };
 int sm100_varlen_bwd128_launch(const Bwd128Launch& L, cudaStream_t s);
+// One-pass backward (head dim 128): dK, dV and the dQ contributions of every score tile from one kernel over
+// the dK/dV tile list, dQ summed in L.dq_acc by reductions in global memory and rounded by a second kernel.
+int sm100_varlen_bwd_fused_launch(const Bwd128Launch& L, cudaStream_t s);
 
 // One CTA waits, with the bounded wait every kernel uses, on an mbarrier that nobody arrives on; when the
 // wait runs out it reports code 1 / site 900 through the status word and returns.

@@ -697,7 +697,7 @@ __global__ void __launch_bounds__(sched_impl::kSchedThreads) bwd_prepare_kernel(
 }
 
 struct BwdWorkspace {
-  size_t hdr_dq, hdr_dkv, items_dq, items_dkv, ld, fold, total;
+  size_t hdr_dq, hdr_dkv, items_dq, items_dkv, ld, fold, dq_acc, total;
   SchedCaps caps_dq, caps_dkv;
   long long ld_stride;
 };
@@ -721,7 +721,10 @@ BwdWorkspace bwd_workspace(const vafa_varlen_args* a, int sms) {
   w.items_dkv = w.items_dq + align_up((size_t)w.caps_dq.cap_items * sizeof(WorkItem), 256);
   w.ld = w.items_dkv + align_up((size_t)w.caps_dkv.cap_items * sizeof(WorkItem), 256);
   w.fold = w.ld + align_up((size_t)a->num_heads * w.ld_stride * sizeof(float2), 256);
-  w.total = w.fold + align_up((size_t)a->total_q * a->num_heads * 64, 256);
+  w.dq_acc = w.fold + align_up((size_t)a->total_q * a->num_heads * 64, 256);
+  // the one-pass backward sums dQ in fp32 here
+  const bool fused = varlen_bwd_mode() == 1 && a->head_dim == 128;
+  w.total = w.dq_acc + (fused ? align_up((size_t)a->total_q * a->num_heads * a->head_dim * sizeof(float), 256) : 0);
   return w;
 }
 
@@ -768,6 +771,11 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.D = D; L.dtype = a->dtype; L.sms = sms;
   L.scale = a->scale; L.status = a->status;
   L.run_dq = 1; L.run_dkv = 1;
+  L.dq_acc = nullptr;
+  if (varlen_bwd_mode() == 1 && D == 128) {
+    L.dq_acc = (float*)(base + ws.dq_acc);
+    return sm100_varlen_bwd_fused_launch(L, s);
+  }
   return sm100_varlen_bwd128_launch(L, s);
 }
 

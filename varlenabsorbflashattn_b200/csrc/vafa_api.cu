@@ -35,6 +35,9 @@ int wait_limit_units() {
   return (int)(u < 1 ? 1 : (u > 0x7fffffffLL ? 0x7fffffffLL : u));
 }
 
+static std::atomic<int> g_varlen_bwd_mode{0};
+int varlen_bwd_mode() { return g_varlen_bwd_mode.load(std::memory_order_relaxed); }
+
 namespace {
 
 bool valid_dtype(int d) { return d == VAFA_F32 || d == VAFA_BF16 || d == VAFA_F16; }
@@ -612,6 +615,12 @@ int vafa_cast_from_f32(const float* src, void* dst, size_t n, int32_t dtype, vaf
 long long vafa_set_wait_limit_cycles(long long cycles) {
   const long long prev = g_wait_limit_cycles.load(std::memory_order_relaxed);
   if (cycles > 0) g_wait_limit_cycles.store(cycles, std::memory_order_relaxed);
+  return prev;
+}
+
+int vafa_set_varlen_bwd_mode(int mode) {
+  const int prev = g_varlen_bwd_mode.load(std::memory_order_relaxed);
+  if (mode == 0 || mode == 1) g_varlen_bwd_mode.store(mode, std::memory_order_relaxed);
   return prev;
 }
 

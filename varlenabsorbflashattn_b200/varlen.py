@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["packed_varlen_attn", "packed_varlen_attn_with_lse", "set_validate_cu_seqlens", "set_impl"]
+__all__ = ["packed_varlen_attn", "packed_varlen_attn_with_lse", "set_validate_cu_seqlens", "set_impl", "set_backward_mode"]
 
 _SUPPORTED_HEAD_DIMS = (16, 32, 64, 128, 256)
 _validate = True
@@ -39,6 +39,22 @@ def set_impl(name: str) -> None:
     """'auto' (default), 'simt' or 'tcgen05': which kernel family the library uses."""
     global _impl
     _impl = _lib.IMPL_NAMES[name.lower()]
+
+
+_BWD_MODES = {"split": 0, "fused": 1}
+
+
+def set_backward_mode(name: str) -> str:
+    """'split' (default): the dQ kernel and the dK/dV kernel, gradients bit-identical from run to run like
+    the reference's.  'fused': one pass over the score tiles for head_dim 128 (five matrix products per tile
+    instead of seven, one exponential per score instead of two); dQ is then summed across key tiles by fp32
+    reductions in global memory and its last bits vary from run to run.  Returns the previous mode."""
+    prev = _lib.load().vafa_set_varlen_bwd_mode(_BWD_MODES[name.lower()])
+    return "fused" if prev == 1 else "split"
+
+
+if os.environ.get("VAFA_BWD_MODE"):
+    set_backward_mode(os.environ["VAFA_BWD_MODE"])
 
 
 def _lengths_to_cu(seqinfo: torch.Tensor) -> torch.Tensor:
