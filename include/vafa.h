@@ -22,7 +22,7 @@ extern "C" {
 #pragma GCC visibility push(default)
 #endif
 
-#define VAFA_ABI_VERSION 2
+#define VAFA_ABI_VERSION 3
 
 enum vafa_dtype { VAFA_F32 = 0, VAFA_BF16 = 1, VAFA_F16 = 2 };
 
@@ -56,7 +56,8 @@ typedef void* vafa_stream_t; /* a cudaStream_t */
  * 25-75, 144-287), which here run on the device inside the call.
  * ------------------------------------------------------------------------------------- */
 typedef struct vafa_varlen_args {
-  /* tensors, row-major contiguous: q/o/do/dq [T_q, H, D]; k/v/dk/dv [T_k, H, D] */
+  /* tensors, row-major contiguous: q/o/do/dq [T_q, H, D]; k/v/dk/dv [T_k, H_kv, D] (H_kv = H unless
+     num_kv_heads says otherwise) */
   const void* q;
   const void* k;
   const void* v;
@@ -85,6 +86,11 @@ typedef struct vafa_varlen_args {
   void* workspace;      /* device scratch, >= vafa_varlen_*_workspace_bytes(), 256-byte aligned */
   size_t workspace_bytes;
   int32_t* status;      /* device, VAFA_STATUS_WORDS int32, may be NULL */
+  int32_t num_kv_heads; /* ABI version 3, last field.  0 or H: one K/V head per query head, as in the reference
+                           (MHA only, triton_fa_varlen_v2/triton_fa_varlen_v2/interface.py:12).  A divisor of H:
+                           grouped-query attention, query head h reads K/V head h / (H / H_kv); dk and dv are
+                           [T_k, H_kv, D], summed over the query heads of a group.  Tensor-core kernels only
+                           (bf16/fp16, head_dim 64 or 128); other shapes return VAFA_ERR_UNSUPPORTED. */
 } vafa_varlen_args;
 
 /* Bytes of scratch built into the library for vafa_varlen_fwd_noalloc() (below). */

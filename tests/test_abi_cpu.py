@@ -34,7 +34,7 @@ def test_every_declared_symbol_is_exported(lib):
 
 
 def test_abi_version(lib):
-    assert lib.vafa_abi_version() == 2
+    assert lib.vafa_abi_version() == 3
 
 
 def test_struct_sizes_match_header():

@@ -349,3 +349,51 @@ def test_fused_backward_mode_leaves_other_head_dims_to_the_kernel_pair():
         vb.set_backward_mode("split")
         V.set_impl("auto")
     _compare(ins, o, lse, grads, torch.float16, True)
+
+
+def _gqa_reference(q, k, v, do, cu_q, cu_k, G, causal):
+    """Oracle for grouped-query attention: K/V heads repeated to one per query head, dK/dV summed per group."""
+    ke, ve = k.repeat_interleave(G, dim=1), v.repeat_interleave(G, dim=1)
+    ro, rlse, rdq, rdk, rdv = varlen_attn_ref_fwd_bwd(q, ke, ve, do, cu_q, cu_k, causal=causal)
+    Tk, H, D = rdk.shape
+    return ro, rlse, rdq, rdk.view(Tk, H // G, G, D).sum(2), rdv.view(Tk, H // G, G, D).sum(2)
+
+
+@pytest.mark.parametrize("H,H_kv,D,dtype,causal", [
+    (8, 2, 128, torch.bfloat16, True), (8, 2, 128, torch.bfloat16, False), (4, 1, 64, torch.float16, True),
+    (6, 3, 128, torch.bfloat16, False), (4, 2, 32, torch.float32, True)])
+def test_grouped_query_heads(H, H_kv, D, dtype, causal):
+    """Fewer K/V heads than query heads (the reference is multi-head only): query head h reads K/V head
+    h // (H // H_kv); dK and dV are sums over the group.  The last case (fp32, head dim 32) runs through the
+    wrapper's head expansion, the others on the tensor-core kernels with the shared heads read in place."""
+    ql, kl = [300, 45, 128, 2, 700], [300, 500, 128, 9, 700]
+    G = H // H_kv
+    torch.manual_seed(7)
+    q, _, _, do, cu_q, cu_k = make_varlen_inputs(ql, kl, H, D, dtype, 7)
+    k = torch.randn(sum(kl), H_kv, D).to(dtype)
+    v = torch.randn(sum(kl), H_kv, D).to(dtype)
+    qg, kg, vg = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    o, lse = vb.packed_varlen_attn_with_lse(qg, kg, vg, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, causal=causal)
+    o.backward(do.to(DEV))
+    torch.cuda.synchronize()
+    assert kg.grad.shape == k.shape and vg.grad.shape == v.shape
+    ro, rlse, rdq, rdk, rdv = _gqa_reference(q, k, v, do, cu_q, cu_k, G, causal)
+    check_close("o", o, ro, dtype)
+    check_lse(lse / LN2, rlse)
+    check_close("dq", qg.grad, rdq, dtype, scale_abs=True)
+    check_close("dk", kg.grad, rdk, dtype, scale_abs=True)
+    check_close("dv", vg.grad, rdv, dtype, scale_abs=True)
+
+
+def test_grouped_query_decode_reads_shared_heads():
+    """Decode shape with multi-query attention: one query row per sequence, 16 query heads on one K/V head,
+    long KV (split across CTAs)."""
+    ql, kl = [1] * 6, [9000, 300, 4097, 12000, 128, 6000]
+    q, _, _, _, cu_q, cu_k = make_varlen_inputs(ql, kl, 16, 128, torch.bfloat16, 9, with_do=False)
+    k = torch.randn(sum(kl), 1, 128).to(torch.bfloat16)
+    v = torch.randn(sum(kl), 1, 128).to(torch.bfloat16)
+    with torch.no_grad():
+        o, lse = vb.packed_varlen_attn_with_lse(q.to(DEV), k.to(DEV), v.to(DEV), cu_seqlens_q=cu_q, cu_seqlens_k=cu_k)
+    ro, rlse = varlen_attn_ref(q, k.repeat_interleave(16, dim=1), v.repeat_interleave(16, dim=1), cu_q, cu_k)
+    check_close("o", o, ro, torch.bfloat16)
+    check_lse(lse / LN2, rlse)

@@ -41,6 +41,7 @@ class VarlenArgs(C.Structure):
         ("num_heads", C.c_int32), ("head_dim", C.c_int32), ("dtype", C.c_int32), ("causal", C.c_int32),
         ("scale", C.c_float), ("impl", C.c_int32), ("split_k_block", C.c_int32), ("sm_count", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("num_kv_heads", C.c_int32),
     ]
 
 
@@ -106,7 +107,7 @@ def load() -> C.CDLL:
         lib.vafa_profile_kernel_name.restype = C.c_char_p
         lib.vafa_profile_read.argtypes = [C.c_int, C.POINTER(C.c_double), C.POINTER(C.c_longlong),
                                           C.POINTER(C.c_longlong)]
-        if lib.vafa_abi_version() != 2:
+        if lib.vafa_abi_version() != 3:
             raise RuntimeError("libvafa_b200.so: ABI version mismatch; rebuild")
         _lib = lib
     return _lib

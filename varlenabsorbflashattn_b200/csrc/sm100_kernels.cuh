@@ -23,6 +23,7 @@ struct Bwd128Launch {
   const void* aug;  // fold array [total_q, H, 32] (dK/dV kernel)
   const void* hdr_dq; const void* items_dq; const void* hdr_dkv; const void* items_dkv;
   int total_q, total_k, H, D, dtype, sms;
+  int H_kv;             // K/V heads (a divisor of H; H for plain multi-head attention)
   float scale;
   int32_t* status;
   int run_dq, run_dkv;  // which of the two kernels to launch

@@ -723,7 +723,7 @@ BwdWorkspace bwd_workspace(const vafa_varlen_args* a, int sms) {
   w.fold = w.ld + align_up((size_t)a->num_heads * w.ld_stride * sizeof(float2), 256);
   w.dq_acc = w.fold + align_up((size_t)a->total_q * a->num_heads * 64, 256);
   // the one-pass backward sums dQ in fp32 here
-  const bool fused = varlen_bwd_mode() == 1 && a->head_dim == 128;
+  const bool fused = varlen_bwd_mode() == 1 && a->head_dim == 128 && (a->num_kv_heads == 0 || a->num_kv_heads == a->num_heads);
   w.total = w.dq_acc + (fused ? align_up((size_t)a->total_q * a->num_heads * a->head_dim * sizeof(float), 256) : 0);
   return w;
 }
@@ -741,8 +741,10 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   sq.header = (SchedHeader*)(base + ws.hdr_dq);
   sq.items = (WorkItem*)(base + ws.items_dq);
   sq.combine = nullptr;
+  const int h_kv = a->num_kv_heads > 0 ? a->num_kv_heads : a->num_heads;
   SchedParams sk = sq;
   sk.mode = kSchedDkv;
+  sk.H = h_kv;  // one dK/dV item per key tile and K/V head; it walks the query rows of all heads of its group
   sk.cap_items = ws.caps_dkv.cap_items;
   sk.header = (SchedHeader*)(base + ws.hdr_dkv);
   sk.items = (WorkItem*)(base + ws.items_dkv);
@@ -768,11 +770,11 @@ int launch_bwd(const vafa_varlen_args* a, cudaStream_t s) {
   L.q = a->q; L.k = a->k; L.v = a->v; L.d_o = a->d_o; L.dq = a->dq; L.dk = a->dk; L.dv = a->dv;
   L.ld = ld; L.ld_stride = ws.ld_stride; L.aug = base + ws.fold;
   L.hdr_dq = sq.header; L.items_dq = sq.items; L.hdr_dkv = sk.header; L.items_dkv = sk.items;
-  L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.D = D; L.dtype = a->dtype; L.sms = sms;
+  L.total_q = a->total_q; L.total_k = a->total_k; L.H = a->num_heads; L.H_kv = h_kv; L.D = D; L.dtype = a->dtype; L.sms = sms;
   L.scale = a->scale; L.status = a->status;
   L.run_dq = 1; L.run_dkv = 1;
   L.dq_acc = nullptr;
-  if (varlen_bwd_mode() == 1 && D == 128) {
+  if (varlen_bwd_mode() == 1 && D == 128 && h_kv == a->num_heads) {
     L.dq_acc = (float*)(base + ws.dq_acc);
     return sm100_varlen_bwd_fused_launch(L, s);
   }

@@ -95,7 +95,9 @@ struct Params128 {
   long long ld_stride;
   const SchedHeader* header;
   const WorkItem* items;
-  int H;
+  int H;      // heads of the outer tensors and of the outputs (dQ kernel: query heads; dK/dV kernel: K/V heads)
+  int group;  // query heads per K/V head: the dQ kernel reads K/V head h / group, the dK/dV kernel walks the
+              // query rows of its `group` query heads one head after the other, into the same accumulators
   float scale;
   float scale_log2;
   int32_t* status;
@@ -193,22 +195,25 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
           tma_load_3d(smem_u32(sm.outer_a) + c * Cfg::kSubBytes, &tmap_outer_a, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
           tma_load_3d(smem_u32(sm.outer_b) + c * Cfg::kSubBytes, &tmap_outer_b, smem_u32(&sm.outer_full), c * 64, h, w.o_start);
         }
-        for (int b = 0; b < nb; ++b, ++gk) {
+        const int nbt = kDKV ? nb * p.group : nb;
+        for (int bb = 0; bb < nbt; ++bb, ++gk) {
           const int sa = gk % SA, sb = gk % SB;
+          const int b = kDKV ? bb % nb : bb;
+          const int hin = kDKV ? h * p.group + bb / nb : h / p.group;  // head of the inner tensors
           const int row = w.i_start + b * kIn;
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.a_empty[sa]), ((gk / SA) & 1) ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(0); }
           mbar_expect_tx(smem_u32(&sm.a_full[sa]), Cfg::kTileBytes + (kDKV ? 2 * kAugBytes : 0));
           for (int c = 0; c < Cfg::kSub; ++c)
-            tma_load_3d(smem_u32(sm.inner_a[sa]) + c * Cfg::kSubBytes, &tmap_inner_a, smem_u32(&sm.a_full[sa]), c * 64, h, row);
+            tma_load_3d(smem_u32(sm.inner_a[sa]) + c * Cfg::kSubBytes, &tmap_inner_a, smem_u32(&sm.a_full[sa]), c * 64, hin, row);
           if (kDKV) {
             // fold pieces of the block's 128 query rows: elements [0,16) for lse, [16,32) for delta
-            tma_load_3d(smem_u32(sm.aug[sa][0]), &tmap_aug, smem_u32(&sm.a_full[sa]), 0, h, row);
-            tma_load_3d(smem_u32(sm.aug[sa][1]), &tmap_aug, smem_u32(&sm.a_full[sa]), 16, h, row);
+            tma_load_3d(smem_u32(sm.aug[sa][0]), &tmap_aug, smem_u32(&sm.a_full[sa]), 0, hin, row);
+            tma_load_3d(smem_u32(sm.aug[sa][1]), &tmap_aug, smem_u32(&sm.a_full[sa]), 16, hin, row);
           }
           { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.b_empty[sb]), ((gk / SB) & 1) ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.b_full[sb]), Cfg::kTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
-            tma_load_3d(smem_u32(sm.inner_b[sb]) + c * Cfg::kSubBytes, &tmap_inner_b, smem_u32(&sm.b_full[sb]), c * 64, h, row);
+            tma_load_3d(smem_u32(sm.inner_b[sb]) + c * Cfg::kSubBytes, &tmap_inner_b, smem_u32(&sm.b_full[sb]), c * 64, hin, row);
         }
         ++qi;
       }
@@ -275,7 +280,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         const int idx = wq_consume_thread(sm.wq, n, abort_flag);
         if (idx < 0) break;
         const WorkItem w = p.items[idx];
-        const int nb = (w.i_len + kIn - 1) / kIn;
+        const int nb = ((w.i_len + kIn - 1) / kIn) * (kDKV ? p.group : 1);  // blocks of the item, over all its query heads
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.outer_full), qi & 1, abort_flag)) break; TRACE_ADD(3); }
         tc_fence_after();
@@ -331,7 +336,8 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
       if (idx < 0) break;
       const WorkItem w = p.items[idx];
       const int h = w.head;
-      const int nb = (w.i_len + kIn - 1) / kIn;
+      const int nb1 = (w.i_len + kIn - 1) / kIn;      // blocks per query head
+      const int nb = nb1 * (kDKV ? p.group : 1);
       const bool row_ok = r < w.o_rows;
       float neg_lse = -INFINITY, my_delta = 0.f;
       if (!kDKV && row_ok && nb > 0) {
@@ -340,8 +346,9 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         my_delta = t.y;
       }
 
-      for (int b = 0; b < nb; ++b) {
-        const uint32_t g = gk + b;
+      for (int bb = 0; bb < nb; ++bb) {
+        const uint32_t g = gk + bb;
+        const int b = kDKV ? bb % nb1 : bb;  // block within the query head's rows
         // visibility of inner index jj = b*128 + col for this thread's outer row r
         //   dQ : jj < i_len and (causal) jj <= r + diag
         //   dKV: jj < i_len and (causal) jj >= r + diag
@@ -538,9 +545,10 @@ static int launch128(const Bwd128Launch& L, cudaStream_t s) {
   int rc;
   if ((rc = encode_tmap_rows(&q128, L.q, L.dtype, L.total_q, L.H, D, 128))) return rc;
   if ((rc = encode_tmap_rows(&do128, L.d_o, L.dtype, L.total_q, L.H, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&k128, L.k, L.dtype, L.total_k, L.H, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&v128, L.v, L.dtype, L.total_k, L.H, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&k128, L.k, L.dtype, L.total_k, L.H_kv, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&v128, L.v, L.dtype, L.total_k, L.H_kv, D, 128))) return rc;
   if ((rc = encode_tmap_fold(&aug, L.aug, L.dtype, L.total_q, L.H))) return rc;
+  p.group = L.H / L.H_kv;
   if (L.run_dq) {
     // dQ: outer = (Q, dO) tiles, inner = (K, V) blocks
     const size_t smem = sizeof(Smem128<D, false>) + 1024;
@@ -556,6 +564,7 @@ static int launch128(const Bwd128Launch& L, cudaStream_t s) {
     // dK/dV: outer = (K, V) tiles, inner = (Q, dO) blocks
     const size_t smem = sizeof(Smem128<D, true>) + 1024;
     p.out0 = L.dv; p.out1 = L.dk; p.header = (const SchedHeader*)L.hdr_dkv; p.items = (const WorkItem*)L.items_dkv;
+    p.H = L.H_kv;
     VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_bwd128_kernel<T, D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     {
       LaunchScope scope(kKBwdDkv, s);

@@ -97,6 +97,7 @@ struct FwdParams {
   const SchedHeader* header;
   const WorkItem* items;
   int H;
+  int group;  // query heads per K/V head (1 = one K/V head per query head)
   float scale_log2;
   int32_t* status;
   int wait_limit;  // bound of every device-side wait, in units of 65536 cycles
@@ -175,6 +176,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if (idx < 0) break;
         const WorkItem w = p.items[idx];
         const int h = w.head;
+        const int hk = kAbsorb ? h : h / p.group;  // K/V head of this query head
         const int nb = (w.i_len + kBlk - 1) / kBlk;
         if (nb == 0) continue;
         { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break; TRACE_ADD(0); }
@@ -188,23 +190,23 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         constexpr int kPrefetch = 4;
         if (kAbsorb)
           for (int b = 2; b < kPrefetch && b < nb; ++b)
-            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, w.i_start + b * kBlk);
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, hk, w.i_start + b * kBlk);
         for (int b = 0; b < nb; ++b, ++gk) {
           const int st = gk % S;
           const uint32_t ph = (gk / S) & 1;
           const int row = w.i_start + b * kBlk;
           if (kAbsorb && b + kPrefetch < nb)
-            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, h, row + kPrefetch * kBlk);
+            for (int c = 0; c < Cfg::kSub; ++c) tma_prefetch_3d(&tmap_k, c * 64, hk, row + kPrefetch * kBlk);
           // slot free: S(gk-2) complete (absorb: P.X(gk-3) complete, the tile doubles as V)
           { TRACE_T0(); if (!mbar_wait(smem_u32(kAbsorb ? &sm.o_done[st] : &sm.s_full[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(1); }
           mbar_expect_tx(smem_u32(&sm.k_full[st]), kKTileBytes);
           for (int c = 0; c < Cfg::kSub; ++c)
-            tma_load_3d(smem_u32(sm.k[st]) + c * kKSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, h, row);
+            tma_load_3d(smem_u32(sm.k[st]) + c * kKSubBytes, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, hk, row);
           if (!kAbsorb) {
             { TRACE_T0(); if (!mbar_wait(smem_u32(&sm.o_done[st]), ph ^ 1, abort_flag)) { alive = false; break; } TRACE_ADD(2); }
             mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
             for (int c = 0; c < Cfg::kSub; ++c)
-              tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, h, row);
+              tma_load_3d(smem_u32(sm.v[st]) + c * Cfg::kSubBytes, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, hk, row);
           }
         }
         ++qi;
@@ -657,8 +659,9 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
 
   CUtensorMap tq, tk, tv;
   if ((rc = encode_tmap_rows(&tq, a->q, a->dtype, a->total_q, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&tk, a->k, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
-  if ((rc = encode_tmap_rows(&tv, a->v, a->dtype, a->total_k, a->num_heads, D, 128))) return rc;
+  const int h_kv = a->num_kv_heads > 0 ? a->num_kv_heads : a->num_heads;
+  if ((rc = encode_tmap_rows(&tk, a->k, a->dtype, a->total_k, h_kv, D, 128))) return rc;
+  if ((rc = encode_tmap_rows(&tv, a->v, a->dtype, a->total_k, h_kv, D, 128))) return rc;
 
   FwdParams p;
   p.wait_limit = wait_limit_units();
@@ -666,6 +669,7 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   p.partial_lse = (float*)(base + ws.plse);
   p.partial_o = (float*)(base + ws.po);
   p.header = sp.header; p.items = sp.items; p.H = a->num_heads;
+  p.group = a->num_heads / h_kv;
   p.scale_log2 = a->scale * kLog2e;
   p.status = a->status;
   p.trace = nullptr;
@@ -737,6 +741,7 @@ int launch_absorb_core_fwd(const AbsorbCoreArgs& a, cudaStream_t s) {
   p.wait_limit = wait_limit_units();
   p.o = a.axn; p.lse = a.lse; p.partial_o = nullptr; p.partial_lse = nullptr;
   p.header = sp.header; p.items = sp.items; p.H = a.H;
+  p.group = 1;
   p.scale_log2 = a.scale * kLog2e;
   p.status = a.status;
   p.trace = nullptr;

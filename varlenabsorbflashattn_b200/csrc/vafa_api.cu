@@ -59,8 +59,13 @@ int check_varlen(const vafa_varlen_args* a, bool bwd) {
   }
   if (a->split_k_block < 0 || (a->split_k_block % 128) != 0)
     return fail(VAFA_ERR_INVALID, "split_k_block %d must be 0 or a multiple of 128", a->split_k_block);
+  if (a->num_kv_heads < 0 || (a->num_kv_heads > 0 && (a->num_heads % a->num_kv_heads) != 0))
+    return fail(VAFA_ERR_INVALID, "num_kv_heads %d must divide num_heads %d", a->num_kv_heads, a->num_heads);
   return 0;
 }
+
+// grouped-query attention (fewer K/V heads than query heads) exists on the tensor-core kernels only
+bool is_gqa(const vafa_varlen_args* a) { return a->num_kv_heads > 0 && a->num_kv_heads != a->num_heads; }
 
 bool varlen_fwd_tc_ok(const vafa_varlen_args* a) { return sm100_varlen_fwd_supported(a); }
 bool varlen_bwd_tc_ok(const vafa_varlen_args* a) { return sm100_varlen_bwd_supported(a); }
@@ -502,6 +507,7 @@ int vafa_varlen_fwd(const vafa_varlen_args* a, vafa_stream_t stream) {
   cudaStream_t s = (cudaStream_t)stream;
   const int impl = pick_impl(a->impl, varlen_fwd_tc_ok(a), "varlen_fwd");
   if (impl < 0) return impl;
+  if (impl == 0 && is_gqa(a)) return fail(VAFA_ERR_UNSUPPORTED, "num_kv_heads != num_heads needs the tcgen05 kernels (bf16/fp16, head_dim 64/128)");
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_varlen_fwd_workspace_bytes(a)))) return rc;
   if (impl == 1) return sm100_varlen_fwd(a, s);
   return simt_attn_fwd(simt_from_varlen(a), s);
@@ -521,6 +527,7 @@ int vafa_varlen_bwd(const vafa_varlen_args* a, vafa_stream_t stream) {
   cudaStream_t s = (cudaStream_t)stream;
   const int impl = pick_impl(a->impl, varlen_bwd_tc_ok(a), "varlen_bwd");
   if (impl < 0) return impl;
+  if (impl == 0 && is_gqa(a)) return fail(VAFA_ERR_UNSUPPORTED, "num_kv_heads != num_heads needs the tcgen05 kernels (bf16/fp16, head_dim 64/128)");
   if ((rc = need_ws(a->workspace, a->workspace_bytes, vafa_varlen_bwd_workspace_bytes(a)))) return rc;
   if (impl == 1) return sm100_varlen_bwd(a, s);
   SimtAttnParams p = simt_from_varlen(a);

@@ -112,6 +112,7 @@ def _fill_args(q, k, v, o, lse, cu_q, cu_k, scale, causal, split_k_block) -> _li
     a.n_seg = cu_q.numel() - 1
     a.total_q, a.num_heads, a.head_dim = q.shape
     a.total_k = k.shape[0]
+    a.num_kv_heads = k.shape[1]
     a.dtype = _lib.DTYPE_CODE[q.dtype]
     a.causal = int(bool(causal))
     a.scale = float(scale)
@@ -128,9 +129,10 @@ class _PackedVarlenAttn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, scale, causal, split_k_block):
         T_q, H, D = q.shape
-        T_k = k.shape[0]
-        assert k.shape == (T_k, H, D), f"K shape mismatch: {tuple(k.shape)} vs expected ({T_k},{H},{D})"
-        assert v.shape == (T_k, H, D), f"V shape mismatch: {tuple(v.shape)} vs expected ({T_k},{H},{D})"
+        T_k, H_kv = k.shape[0], k.shape[1]
+        assert k.dim() == 3 and k.shape[2] == D and H_kv >= 1 and H % H_kv == 0, \
+            f"K shape mismatch: {tuple(k.shape)} vs expected ({T_k},{H},{D}) (or fewer heads dividing {H})"
+        assert v.shape == k.shape, f"V shape mismatch: {tuple(v.shape)} vs K {tuple(k.shape)}"
         assert q.dtype == k.dtype == v.dtype, "q/k/v must share dtype"
         assert q.dtype in _lib.DTYPE_CODE, f"q/k/v must be fp32, bf16 or fp16, got {q.dtype}"
         assert q.is_cuda, "packed_varlen_attn requires CUDA tensors (there is no CPU path)"
@@ -191,6 +193,8 @@ def _prepare(q, k, v, cu_seqlens_q, cu_seqlens_k, q_seqinfo, k_seqinfo, scale):
         cu_seqlens_k = _lengths_to_cu(k_seqinfo)
     if scale is None:
         scale = 1.0 / math.sqrt(q3.shape[-1])
+    if k3.dim() == 3 and q3.dim() == 3 and k3.shape[1] != q3.shape[1]:
+        k3, v3 = _expand_kv_heads(q3, k3, v3)
     return q3, k3, v3, cu_seqlens_q, cu_seqlens_k, float(scale), q4
 
 
@@ -210,6 +214,9 @@ def packed_varlen_attn(
     """Attention where token t of segment i attends only to the keys of segment i.
 
     q: [1, T_q, H, D] or [T_q, H, D]; k, v: [1, T_k, H, D] or [T_k, H, D] (fp32, bf16 or fp16).
+    k and v may carry fewer heads, H_kv dividing H (grouped-query / multi-query attention; the reference is
+    multi-head only): query head h then attends over K/V head h // (H // H_kv), and dk, dv come back with
+    H_kv heads.
     cu_seqlens_q / cu_seqlens_k: [n_seg+1] prefix sums (any integer dtype, any device), or
     q_seqinfo / k_seqinfo: [n_seg] per-segment lengths.  scale defaults to 1/sqrt(D).
     causal: bottom-right aligned causal mask inside each segment (row i sees keys
@@ -229,6 +236,20 @@ def packed_varlen_attn(
     q3, k3, v3, cu_q, cu_k, scale, was4 = _prepare(q, k, v, cu_seqlens_q, cu_seqlens_k, q_seqinfo, k_seqinfo, scale)
     o, _ = _PackedVarlenAttn.apply(q3, k3, v3, cu_q, cu_k, scale, bool(causal), split_k_block)
     return o.unsqueeze(0) if was4 else o
+
+
+def _expand_kv_heads(q3, k3, v3):
+    """Grouped-query inputs on shapes the tensor-core kernels do not take (fp32, head dims other than 64/128):
+    the K/V heads are repeated to one per query head with a differentiable torch op, so the gradients come back
+    summed over each group.  The tensor-core kernels read the shared heads in place instead."""
+    H, H_kv = q3.shape[1], k3.shape[1]
+    if H_kv == H or H % max(H_kv, 1) != 0:
+        return k3, v3
+    native = q3.dtype in (torch.bfloat16, torch.float16) and q3.shape[2] in (64, 128) and _impl != _lib.IMPL_SIMT
+    if native:
+        return k3, v3
+    g = H // H_kv
+    return k3.repeat_interleave(g, dim=1), v3.repeat_interleave(g, dim=1)
 
 
 def packed_varlen_attn_with_lse(q, k, v, *, cu_seqlens_q=None, cu_seqlens_k=None, q_seqinfo=None,
