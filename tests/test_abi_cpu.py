@@ -38,8 +38,8 @@ def test_abi_version(lib):
 
 
 def test_struct_sizes_match_header():
-    # 11 pointers + 7 int32 + float + 3 int32 (+pad) + pointer + size_t + pointer
-    assert C.sizeof(_lib.VarlenArgs) == 11 * 8 + 12 * 4 + 3 * 8
+    # 11 pointers + 7 int32 + float + 3 int32 (+pad) + pointer + size_t + pointer + num_kv_heads (int32, padded to 8)
+    assert C.sizeof(_lib.VarlenArgs) == 11 * 8 + 12 * 4 + 3 * 8 + 8
     # ... + x_width (int32, padded to 8)
     assert C.sizeof(_lib.AbsorbArgs) == 14 * 8 + 12 * 4 + 3 * 8 + 8
 
@@ -91,3 +91,13 @@ def test_absorb_narrow_x_needs_a_valid_width(lib):
     a.x_width = 216
     assert lib.vafa_absorb_fwd(C.byref(a), None) == -2
     assert b"tcgen05" in lib.vafa_last_error()
+
+
+def test_kv_head_count_must_divide_the_query_heads(lib):
+    a = _lib.VarlenArgs()
+    a.n_seg, a.total_q, a.total_k, a.num_heads, a.head_dim, a.dtype = 1, 0, 0, 6, 64, 1
+    cu = (C.c_int32 * 2)(0, 0)
+    a.cu_seqlens_q = a.cu_seqlens_k = C.cast(cu, C.c_void_p)
+    a.num_kv_heads = 4
+    assert lib.vafa_varlen_fwd(C.byref(a), None) == -1
+    assert b"num_kv_heads" in lib.vafa_last_error()
