@@ -47,8 +47,13 @@ def _digest() -> str:
             h.update(f.encode())
             with open(p, "rb") as fh:
                 h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _extra_flags()).encode())
     return h.hexdigest()
+
+
+def _extra_flags() -> list[str]:
+    """Additional nvcc flags from VAFA_NVCC_FLAGS (e.g. -DVAFA_BWD_EW_WARPS=16), for experiments."""
+    return os.environ.get("VAFA_NVCC_FLAGS", "").split()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
@@ -62,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(src: str) -> str:
         obj = os.path.join(BUILD_DIR, os.path.basename(src)[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *_extra_flags(), "-c", src, "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

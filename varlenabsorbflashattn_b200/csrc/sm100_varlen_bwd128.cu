@@ -46,7 +46,20 @@ using namespace ptx;
 #define TRACE_ADD(slot)
 #endif
 
-constexpr int kThreads = 320;  // 8 element-wise warps, 1 TMA warp, 1 MMA warp
+// Element-wise warps: 8 (two per TMEM lane quadrant, 64 score columns per thread) or 16 (four per quadrant, 32
+// columns per thread).  The backward needs no row statistics, so the columns of a row split freely.
+#ifndef VAFA_BWD_EW_WARPS
+#define VAFA_BWD_EW_WARPS 8
+#endif
+constexpr int kEw = VAFA_BWD_EW_WARPS;
+static_assert(kEw == 8 || kEw == 16, "element-wise warps");
+constexpr int kGroups = kEw / 4;        // column groups of a row
+constexpr int kC = 128 / kGroups;       // score columns per thread
+constexpr int kTmaWarp = kEw, kMmaWarp = kEw + 1;
+constexpr int kThreads = kEw * 32 + 64;  // + 1 TMA warp, 1 MMA warp
+// one tcgen05.ld for a thread's kC columns
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 constexpr int kIn = 128;       // rows per inner block
 constexpr int kPolyPeriod = 4;  // one pair in four computes 2^t by polynomial
 constexpr int kAugBytes = 128 * 32;  // one fold tile: 128 rows x 16 elements, 32-byte swizzle
@@ -124,7 +137,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
   if (threadIdx.x == 0) {
     sm.abort_flag = 0;
     sm.wait_limit = p.wait_limit;
-    wq_init(sm.wq, 9);
+    wq_init(sm.wq, kEw + 1);
     mbar_init(smem_u32(&sm.outer_full), 1);
     mbar_init(smem_u32(&sm.outer_free), 1);
     for (int i = 0; i < SA; ++i) {
@@ -138,27 +151,27 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
     mbar_init(smem_u32(&sm.x_full[0]), 1);
     mbar_init(smem_u32(&sm.x_full[1]), 1);
     mbar_init(smem_u32(&sm.y_full), 1);
-    mbar_init(smem_u32(&sm.p_full), 8);   // one arrival per element-wise warp
-    mbar_init(smem_u32(&sm.ds_full), 8);
+    mbar_init(smem_u32(&sm.p_full), kEw);   // one arrival per element-wise warp
+    mbar_init(smem_u32(&sm.ds_full), kEw);
     mbar_init(smem_u32(&sm.acc_done), 1);
     fence_barrier_init();
   }
-  if (kDKV && warp < 8) {
+  if (kDKV && warp < kEw) {
     // the constant operand of the fold step: every element 1 (bf16) or 64 (fp16, whose pieces are
     // stored divided by 64 to keep them in range); uniform, so the swizzle does not matter
     const uint32_t one2 = std::is_same<T, __nv_bfloat16>::value ? 0x3F803F80u : 0x54005400u;
     uint32_t* o32 = reinterpret_cast<uint32_t*>(sm.ones);
-    for (int i = threadIdx.x; i < kAugBytes / 4; i += 256) o32[i] = one2;
+    for (int i = threadIdx.x; i < kAugBytes / 4; i += kEw * 32) o32[i] = one2;
     fence_proxy_async();
   }
-  if (warp == 8 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     prefetch_tensormap(&tmap_outer_a);
     prefetch_tensormap(&tmap_outer_b);
     prefetch_tensormap(&tmap_inner_a);
     prefetch_tensormap(&tmap_inner_b);
     if (kDKV) prefetch_tensormap(&tmap_aug);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sm.tmem_base), 512);
     tmem_relinquish();
   }
@@ -177,7 +190,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
   const long long t_begin = clock64();
 #endif
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
@@ -218,7 +231,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         ++qi;
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -326,7 +339,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
     // thread -> outer row r = tid % 128 (TMEM lane; a warp may only touch lane quadrant warp % 4);
     // warps 0-3 take inner columns [0,64) of every block, warps 4-7 columns [64,128)
     const int r = threadIdx.x & 127;
-    const int half = threadIdx.x >> 7;
+    const int grp = threadIdx.x >> 7;  // column group of this thread
     const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
     const float c = p.scale_log2;
     uint32_t gk = 0, qi = 0;
@@ -367,20 +380,20 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
 #ifdef VAFA_TRACE
         const long long t_p1 = clock64();
 #endif
-        float pf[64];
+        float pf[kC];
         // masked blocks (tails, the causal diagonal) take their own copy of the loop: folded into one
         // loop the two compares and the select per element ran in every block
         auto phase1 = [&](auto mask_tag) {
           constexpr bool kMask = decltype(mask_tag)::value;
-          // this thread's 64 columns [64*half, 64*half + 64) in one load
-          uint32_t xs[64];
-          tmem_ld64(x_addr + half * 64, xs);
+          // this thread's columns [kC * grp, kC * grp + kC) in one load
+          uint32_t xs[kC];
+          tmem_ld_cols(x_addr + grp * kC, xs);
           tmem_wait_ld();
           // exponent t = c X' (dK/dV: the product already holds S - lse/c) or c S - lse, in pairs; every
           // kPolyPeriod-th pair takes the polynomial 2^t on the FMA pipe, the others the special-function unit
           const uint64_t c2 = pack_f2(c, c), nl2 = pack_f2(neg_lse, neg_lse);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < kC / 2; ++i) {
             const uint64_t x2 = pack_f2(__uint_as_float(xs[2 * i]), __uint_as_float(xs[2 * i + 1]));
             const uint64_t t2 = kDKV ? mul_f2(x2, c2) : fma_f2(x2, c2, nl2);
             float p0, p1;
@@ -393,7 +406,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
               p1 = ex2(t1);
             }
             if (kMask) {
-              const int col = half * 64 + 2 * i;
+              const int col = grp * kC + 2 * i;
               p0 = ((col >= lo) && (col <= hi)) ? p0 : 0.f;
               p1 = ((col + 1 >= lo) && (col + 1 <= hi)) ? p1 : 0.f;
             }
@@ -403,11 +416,11 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
           if (kDKV) {
             // P^T in place: each 32-column chunk becomes 16 packed columns over its own first half
 #pragma unroll
-            for (int q2 = 0; q2 < 2; ++q2) {
+            for (int q2 = 0; q2 < kC / 32; ++q2) {
               uint32_t pp[16];
 #pragma unroll
               for (int i = 0; i < 16; ++i) pp[i] = pack2<T>(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]);
-              tmem_st16(x_addr + (half * 2 + q2) * 32, pp);
+              tmem_st16(x_addr + (grp * (kC / 32) + q2) * 32, pp);
             }
           }
         };
@@ -430,12 +443,12 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         const long long t_p2 = clock64();
 #endif
         {
-          uint32_t ys[64];
+          uint32_t ys[kC];
           const uint64_t nd2 = pack_f2(-my_delta, -my_delta);
-          tmem_ld64(y_addr + half * 64, ys);
+          tmem_ld_cols(y_addr + grp * kC, ys);
           tmem_wait_ld();
 #pragma unroll
-          for (int q2 = 0; q2 < 2; ++q2) {
+          for (int q2 = 0; q2 < kC / 32; ++q2) {
             uint32_t dd[16];
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
@@ -448,7 +461,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
               dd[i] = pack2<T>(d0, d1);
             }
             // dQ: dS over the scores just consumed (X[g&1]); dK/dV: dS^T over dP^T (Y); in place as above
-            tmem_st16((kDKV ? y_addr : x_addr) + (half * 2 + q2) * 32, dd);
+            tmem_st16((kDKV ? y_addr : x_addr) + (grp * (kC / 32) + q2) * 32, dd);
           }
         }
         tmem_wait_st();
@@ -481,8 +494,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
         const float mul = (kDKV && which == 0) ? 1.f : ((!kDKV && neg_lse == -INFINITY) ? 0.f : p.scale + poison);
         const uint32_t acc_col = which == 0 ? Cfg::kAcc0 : Cfg::kAcc1;
 #pragma unroll
-        for (int c2 = 0; c2 < D / 64; ++c2) {
-          const int cc = half * (D / 64) + c2;
+        for (int cc = grp; cc < D / 32; cc += kGroups) {  // 32-column chunks of the accumulator, dealt to the groups
           uint32_t t[32];
           if (nb > 0) {
             tmem_ld32(lane_base + acc_col + cc * 32, t);
@@ -516,7 +528,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
     while (clock64() - t0 < 200000) { }
     __syncthreads();
   }
-  if (warp == 9) tmem_dealloc(tbase, 512);
+  if (warp == kMmaWarp) tmem_dealloc(tbase, 512);
 }
 
 }  // namespace
