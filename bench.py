@@ -341,12 +341,12 @@ def production_lengths(seed=0):
     return [int(x) for x in q], [int(x) for x in k]
 
 
-def absorb_inputs(ql, kl, d_q, d_kv, dev, seed=0):
+def absorb_inputs(ql, kl, d_q, d_kv, dev, seed=0, dtype=torch.bfloat16):
     Tq, Tk = sum(ql), sum(kl)
-    q_raw = device_randn((Tq, d_q), seed * 16 + 1, dev)
-    X = device_randn((Tk, d_kv), seed * 16 + 2, dev)
-    W = [device_randn((d, 8, 32), seed * 16 + 3 + i, dev, std=1 / 16) for i, d in enumerate((d_q, d_kv, d_kv))]
-    dO = device_randn((Tq, 8, 32), seed * 16 + 6, dev)
+    q_raw = device_randn((Tq, d_q), seed * 16 + 1, dev, dtype)
+    X = device_randn((Tk, d_kv), seed * 16 + 2, dev, dtype)
+    W = [device_randn((d, 8, 32), seed * 16 + 3 + i, dev, dtype, std=1 / 16) for i, d in enumerate((d_q, d_kv, d_kv))]
+    dO = device_randn((Tq, 8, 32), seed * 16 + 6, dev, dtype)
     return q_raw, X, W, dO
 
 
@@ -490,8 +490,8 @@ def compare_leg():
                                           "fwd_bwd": round(d[who]["fwd_bwd_ms"] / d["ours"]["fwd_bwd_ms"], 3)}
         res[name] = out
 
-    def absorb_case(name, ql, kl, d_q, d_kv):
-        q_raw, X, W, dO = absorb_inputs(ql, kl, d_q, d_kv, dev)
+    def absorb_case(name, ql, kl, d_q, d_kv, dtype=torch.bfloat16):
+        q_raw, X, W, dO = absorb_inputs(ql, kl, d_q, d_kv, dev, dtype=dtype)
         q_raw.requires_grad_(True); X.requires_grad_(True)
         W = [w.requires_grad_(True) for w in W]
         cu_q, cu_k = lengths_to_cu(ql).to(dev), lengths_to_cu(kl).to(dev)
@@ -522,6 +522,10 @@ def compare_leg():
     absorb_case("C4", ql, kl, 256, 256)
     ql, kl = production_lengths(0)
     absorb_case("absorb_production_shape", ql, kl, 968, 216)
+    # fp32 inputs are the reference's default for packed_target_attn (IEEE fp32 dots in its kernels); here they
+    # run on the scalar kernels
+    ql, kl = config_lengths("C4", 0)
+    absorb_case("C4_fp32", ql[:256], kl[:256], 256, 256, dtype=torch.float32)
     res["note"] = ("ratios are reference time / this library's time (> 1: this library is faster); the reference has no "
                    "causal mode, so causal is compared with flash-attn only; shapes whose tensors reach 2^31 elements "
                    "(C3, C5) are not run on the reference: its 32-bit indexing faulted there")

@@ -12,7 +12,8 @@ import threading
 import torch
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libvafa_b200.so")
+# VAFA_LIB_PATH points at a library built elsewhere (another build variant, an installed copy)
+LIB_PATH = os.environ.get("VAFA_LIB_PATH") or os.path.join(_PKG, "libvafa_b200.so")
 
 VAFA_F32, VAFA_BF16, VAFA_F16 = 0, 1, 2
 IMPL_AUTO, IMPL_SIMT, IMPL_TCGEN05 = 0, 1, 2

@@ -61,7 +61,17 @@ constexpr int kThreads = kEw * 32 + 64;  // + 1 TMA warp, 1 MMA warp
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
 constexpr int kIn = 128;       // rows per inner block
-constexpr int kPolyPeriod = 4;  // one pair in four computes 2^t by polynomial
+// One pair of exponentials in kPolyPeriod can take the polynomial 2^t on the FMA pipe instead of the
+// special-function unit; 0 = none.  In these kernels none is fastest (measured: period 4 costs 3-5 % on long
+// non-causal batches and 2.5 % on the 1 M-token causal batch): per score they already issue five integer-pipe
+// instructions (two rounding adds and a byte permute for each of P and dS), that pipe runs at half rate and is
+// the busiest one, and the polynomial adds six more per pair.  The forward, with one rounding per score,
+// keeps period 4.
+#ifndef VAFA_BWD_POLY_PERIOD
+#define VAFA_BWD_POLY_PERIOD 0
+#endif
+constexpr int kPolyPeriod = VAFA_BWD_POLY_PERIOD;
+constexpr bool use_poly(int i) { return kPolyPeriod > 0 && (i % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == kPolyPeriod - 1; }
 constexpr int kAugBytes = 128 * 32;  // one fold tile: 128 rows x 16 elements, 32-byte swizzle
 
 template <int D, bool kDKV>
@@ -397,7 +407,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
             const uint64_t x2 = pack_f2(__uint_as_float(xs[2 * i]), __uint_as_float(xs[2 * i + 1]));
             const uint64_t t2 = kDKV ? mul_f2(x2, c2) : fma_f2(x2, c2, nl2);
             float p0, p1;
-            if (i % kPolyPeriod == kPolyPeriod - 1) {
+            if (use_poly(i)) {
               ex2_poly2(t2, p0, p1);
             } else {
               float t0, t1;

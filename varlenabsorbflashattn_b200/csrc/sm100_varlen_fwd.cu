@@ -42,7 +42,10 @@ using namespace ptx;
 
 constexpr int kFwdThreads = 320;  // 8 softmax warps, 1 TMA warp, 1 MMA warp
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-constexpr int kPolyPeriod = 4;             // one pair of exponentials in four runs as a polynomial on the FMA pipe
+#ifndef VAFA_FWD_POLY_PERIOD
+#define VAFA_FWD_POLY_PERIOD 4
+#endif
+constexpr int kPolyPeriod = VAFA_FWD_POLY_PERIOD;  // one pair of exponentials in this many runs as a polynomial on the FMA pipe
 
 template <int D>
 struct FwdCfg {
