@@ -52,7 +52,13 @@ using namespace ptx;
 constexpr int kThreads = 448;
 constexpr int kIn = 128;        // query rows per inner block
 constexpr int kD = 128;         // head dim
-constexpr int kPolyPeriod = 4;  // one pair of exponentials in four runs as a polynomial on the FMA pipe
+// Exponentials as in the kernel pair (all on the special-function unit unless VAFA_BWD_POLY_PERIOD says
+// otherwise), so that dK and dV of the two modes stay bit-identical.
+#ifndef VAFA_BWD_POLY_PERIOD
+#define VAFA_BWD_POLY_PERIOD 0
+#endif
+constexpr int kPolyPeriod = VAFA_BWD_POLY_PERIOD;
+constexpr bool use_poly(int i) { return kPolyPeriod > 0 && (i % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == kPolyPeriod - 1; }
 constexpr int kAugBytes = 128 * 32;
 constexpr int kSubBytes = 128 * 128;      // one 64-column sub tile: 128 rows x 128 B
 constexpr int kTileBytes = 2 * kSubBytes; // 128 rows x 128 columns of 16 bit
@@ -415,7 +421,7 @@ varlen_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
           for (int i = 0; i < 32; ++i) {
             const uint64_t t2 = mul_f2(pack_f2(__uint_as_float(xs[2 * i]), __uint_as_float(xs[2 * i + 1])), c2);
             float p0, p1;
-            if (i % kPolyPeriod == kPolyPeriod - 1) {
+            if (use_poly(i)) {
               ex2_poly2(t2, p0, p1);
             } else {
               float t0, t1;
