@@ -397,3 +397,19 @@ def test_grouped_query_decode_reads_shared_heads():
     ro, rlse = varlen_attn_ref(q, k.repeat_interleave(16, dim=1), v.repeat_interleave(16, dim=1), cu_q, cu_k)
     check_close("o", o, ro, torch.bfloat16)
     check_lse(lse / LN2, rlse)
+
+
+def test_two_tile_forward_kernel_opt_in():
+    """VAFA_FWD_PAIR=1 (read once per process) sends batches of long query segments to the forward kernel that
+    works on two 128-row query tiles per CTA; the reference's shape cases, the split-K cases and the ragged
+    causal cases must pass with it exactly as with the default kernel."""
+    import subprocess
+    env = dict(os.environ, VAFA_FWD_PAIR="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sel = ("(test_reference_cases_bf16 or test_split_k_invariance or test_ragged_random_causal_fwd_bwd "
+           "or test_dtypes_and_head_dims or test_grouped_query_heads) and not simt")
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_varlen_gpu.py"), "-q", "-x",
+                        "-m", "gpu", "-k", sel, "-p", "no:cacheprovider"],
+                       env=env, cwd=root, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout

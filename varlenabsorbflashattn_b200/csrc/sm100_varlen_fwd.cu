@@ -18,6 +18,7 @@
 // P rounded to the I/O dtype before P.V, fp32 row sums from the unrounded P, O = acc / l,
 // LSE = m + log2(l).
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -546,6 +547,436 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
   if (warp == 9) tmem_dealloc(tbase, Cfg::kTmemCols);
 }
 
+// ---------------- two query tiles per CTA --------------------------------------------------------
+// The same operator for batches of long query segments (head dim 64 / 128): an item is a tile of up to 256
+// query rows of one head, worked on as two 128-row tiles A and B against one K/V ring.
+//   warps 0-3  softmax + epilogue of tile A, warps 4-7 of tile B: one thread per query row (TMEM lane = row)
+//              with all 128 score columns of a block, so a row's maximum and sum need no exchange
+//   warp 8     TMA producer, warp 9 tcgen05.mma issuer, as above
+// TMEM: S_A [0,128), S_B [128,256) (one score buffer per tile; P overwrites its first 64 columns),
+// O_A [256,256+D), O_B [256+D,256+2D).  Per block the issuer runs  P_A.V, S_A(next), P_B.V, S_B(next):  while
+// the tensor pipe works for one tile the other tile's threads run their exponentials, and the fixed cost of a
+// block (TMEM round trips, barriers) is paid once per 128 scores of a thread instead of once per 64.
+// Under the causal mask tile A ends one block before tile B; barriers of a tile are indexed by the tile's own
+// block count.
+// Opt-in (environment variable VAFA_FWD_PAIR=1, read once per process): measured on a B200 it is 4 % faster than
+// the one-tile kernel above on long non-causal segments (8 x 8192: 4.40 against 4.60 ms), 6-14 % slower on
+// causal batches (tile A idles through tile B's last block of every item) and on batches of short segments
+// (half as many items, so the scheduler splits keys more often), and level on the 500-query production shapes.
+template <int D>
+struct PairSmem {
+  alignas(1024) uint8_t q[2][FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t k[2][FwdCfg<D>::kTileBytes];
+  alignas(1024) uint8_t v[2][FwdCfg<D>::kTileBytes];
+  alignas(8) uint64_t q_full, q_free;
+  uint64_t k_full[2], v_full[2];
+  uint64_t s_full[2][2], p_full[2][2];  // [tile][the tile's block count & 1], phase (count / 2) & 1
+  uint64_t o_done[2];                   // P.V of both tiles for block g complete: index g & 1 of the K/V ring
+  uint64_t o_ready[2];                  // [tile] the tile's last P.V of an item complete
+  WorkQueue wq;
+  uint32_t tmem_base;
+  int abort_flag;
+  int wait_limit;  // read by the bounded waits as abort_flag[1]: keep it right behind abort_flag
+};
+static_assert(sizeof(PairSmem<128>) + 1024 <= 227 * 1024, "shared memory budget");
+
+// Blocks of an item per tile.  Row r of tile t (row 128 t + r of the item) sees inner index jj iff
+// jj < i_len and (masked) jj <= 128 t + r + diag.
+struct PairShape {
+  int nb, nb_t[2], rows_t[2];
+};
+__device__ __forceinline__ PairShape pair_shape(const WorkItem& w) {
+  PairShape z;
+  z.nb = (w.i_len + kTile - 1) / kTile;
+  z.rows_t[0] = min(kTile, w.o_rows);
+  z.rows_t[1] = max(0, w.o_rows - kTile);
+  const int seen_a = w.masked ? min(w.i_len, z.rows_t[0] + w.diag) : w.i_len;  // keys the last row of A sees
+  z.nb_t[0] = max(0, (seen_a + kTile - 1) / kTile);
+  z.nb_t[1] = z.rows_t[1] > 0 ? z.nb : 0;
+  return z;
+}
+
+// Registers: a softmax thread holds the 128 scores of its row.  The launch gives every thread 168 registers
+// (twelve warps; registers are granted per four warps); the producer / issuer warp group hands most of its
+// share to the two softmax warp groups (setmaxnreg), which then have 216 each.
+#ifndef VAFA_FWD_PAIR_SETMAXNREG
+#define VAFA_FWD_PAIR_SETMAXNREG 1
+#endif
+constexpr int kPairThreads = VAFA_FWD_PAIR_SETMAXNREG ? 384 : kFwdThreads;
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPairThreads, 1)
+varlen_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int kSubB = Cfg::kSubBytes;
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = PairSmem<D>;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sm.abort_flag;
+
+  if (threadIdx.x == 0) {
+    sm.abort_flag = 0;
+    sm.wait_limit = p.wait_limit;
+    wq_init(sm.wq, 9);
+    mbar_init(smem_u32(&sm.q_full), 1);
+    mbar_init(smem_u32(&sm.q_free), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm.k_full[i]), 1);
+      mbar_init(smem_u32(&sm.v_full[i]), 1);
+      mbar_init(smem_u32(&sm.o_done[i]), 1);
+      mbar_init(smem_u32(&sm.o_ready[i]), 1);
+      for (int j = 0; j < 2; ++j) {
+        mbar_init(smem_u32(&sm.s_full[i][j]), 1);
+        mbar_init(smem_u32(&sm.p_full[i][j]), 4);  // lane 0 of each of the tile's four warps
+      }
+    }
+    fence_barrier_init();
+  }
+  if (warp == 8 && lane == 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+  }
+  if (warp == 9) {
+    tmem_alloc(smem_u32(&sm.tmem_base), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tbase = sm.tmem_base;
+
+  const int n_items = p.header->n_items;
+  const int total = max(n_items, 0);
+  int* const next_item = const_cast<int*>(&p.header->next_item);
+  if (n_items < 0 && threadIdx.x == 0) report_error(p.status, 2, 110, n_items);
+
+  // (each setmaxnreg sits inside its own role's branch: after a join of the two the compiler would have to
+  // assume the smaller budget for everything that follows)
+  if (warp >= 10) {
+    // the two spare warps of the third warp group
+#if VAFA_FWD_PAIR_SETMAXNREG
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+#endif
+  } else if (warp == 8) {
+#if VAFA_FWD_PAIR_SETMAXNREG
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+#endif
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t gk = 0, qi = 0, cnt[2] = {0, 0};
+      // what frees a K slot: the last score product issued for the block that used it
+      uint32_t rel_bar[2] = {0, 0}, rel_par[2] = {0, 0};
+      bool alive = true;
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_produce(sm.wq, n, next_item, total, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
+        const PairShape z = pair_shape(w);
+        if (z.nb == 0) continue;
+        const int hk = w.head / p.group;
+        const bool has_b = z.rows_t[1] > 0;
+        if (!mbar_wait(smem_u32(&sm.q_free), (qi & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(smem_u32(&sm.q_full), (has_b ? 2 : 1) * Cfg::kTileBytes);
+        for (int t = 0; t < (has_b ? 2 : 1); ++t)
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.q[t]) + c * kSubB, &tmap_q, smem_u32(&sm.q_full), c * 64, w.head, w.o_start + t * kTile);
+        for (int b = 0; b < z.nb; ++b, ++gk) {
+          const int st = gk & 1;
+          const uint32_t ph = (gk >> 1) & 1;
+          const int row = w.i_start + b * kTile;
+          if (rel_bar[st] != 0 && !mbar_wait(rel_bar[st], rel_par[st], abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.k_full[st]), Cfg::kTileBytes);
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.k[st]) + c * kSubB, &tmap_k, smem_u32(&sm.k_full[st]), c * 64, hk, row);
+          const int t_last = has_b ? 1 : 0;  // tile B runs every block of the item when it exists
+          rel_bar[st] = smem_u32(&sm.s_full[t_last][cnt[t_last] & 1]);
+          rel_par[st] = (cnt[t_last] >> 1) & 1;
+          if (b < z.nb_t[0]) ++cnt[0];
+          if (has_b) ++cnt[1];
+          if (!mbar_wait(smem_u32(&sm.o_done[st]), ph ^ 1, abort_flag)) { alive = false; break; }
+          mbar_expect_tx(smem_u32(&sm.v_full[st]), Cfg::kTileBytes);
+          for (int c = 0; c < Cfg::kSub; ++c)
+            tma_load_3d(smem_u32(sm.v[st]) + c * kSubB, &tmap_v, smem_u32(&sm.v_full[st]), c * 64, hk, row);
+        }
+        ++qi;
+      }
+    }
+  } else if (warp == 9) {
+#if VAFA_FWD_PAIR_SETMAXNREG
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+#endif
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+      constexpr uint32_t idesc_qk = make_idesc(kFmt, 0, 0, 128, kTile);
+      constexpr uint32_t idesc_pv = make_idesc(kFmt, 0, 1, 128, D);
+      uint32_t gk = 0, qi = 0, cnt[2] = {0, 0};
+      bool alive = true;
+
+      // S_t = Q_t K(g)^T, announced on the tile's barrier for its block count c
+      auto issue_s = [&](int t, uint32_t g, uint32_t c) {
+        const uint32_t q_lo = desc_lo_sw128(smem_u32(sm.q[t]), 16), k_lo = desc_lo_sw128(smem_u32(sm.k[g & 1]), 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * (kSubB >> 4) + (kk & 3) * 2;
+          mma_ss2(tbase + t * kTile, q_lo + off, k_lo + off, idesc_qk, kk > 0);
+        }
+        mma_commit(smem_u32(&sm.s_full[t][c & 1]));
+      };
+      // O_t (+)= P_t V(g); P sits in the first 64 columns of the tile's score buffer, two keys per column
+      auto issue_pv = [&](int t, uint32_t g, bool first) {
+        const uint32_t v_lo = desc_lo_sw128(smem_u32(sm.v[g & 1]), kSubB);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          mma_ts2(tbase + Cfg::kOCol + t * D, tbase + t * kTile + kk * 8, v_lo + kk * (2048 >> 4), idesc_pv,
+                  (!first || kk > 0) ? 1u : 0u);
+      };
+
+      for (uint32_t n = 0; alive; ++n) {
+        const int idx = wq_consume_thread(sm.wq, n, abort_flag);
+        if (idx < 0) break;
+        const WorkItem w = p.items[idx];
+        const PairShape z = pair_shape(w);
+        if (z.nb == 0) continue;
+        const bool has_b = z.rows_t[1] > 0;
+        const int t_last = has_b ? 1 : 0;
+        if (!mbar_wait(smem_u32(&sm.q_full), qi & 1, abort_flag)) break;
+        if (!mbar_wait(smem_u32(&sm.k_full[gk & 1]), (gk >> 1) & 1, abort_flag)) break;
+        tc_fence_after();
+        for (int t = 0; t < 2; ++t)
+          if (z.nb_t[t] > 0) issue_s(t, gk, cnt[t]);
+        if (z.nb == 1) mma_commit(smem_u32(&sm.q_free));
+        for (int b = 0; b < z.nb && alive; ++b) {
+          const uint32_t g = gk + b;
+          bool v_ready = false, k_ready = false;
+          for (int t = 0; t < 2; ++t) {
+            if (b >= z.nb_t[t]) continue;
+            const uint32_t c = cnt[t];
+            if (!mbar_wait(smem_u32(&sm.p_full[t][c & 1]), (c >> 1) & 1, abort_flag)) { alive = false; break; }
+            if (!v_ready) {
+              if (!mbar_wait(smem_u32(&sm.v_full[g & 1]), (g >> 1) & 1, abort_flag)) { alive = false; break; }
+              v_ready = true;
+            }
+            tc_fence_after();
+            issue_pv(t, g, b == 0);
+            if (t == t_last) mma_commit(smem_u32(&sm.o_done[g & 1]));
+            if (b + 1 == z.nb_t[t]) mma_commit(smem_u32(&sm.o_ready[t]));
+            ++cnt[t];
+            if (b + 1 < z.nb_t[t]) {
+              if (!k_ready) {
+                if (!mbar_wait(smem_u32(&sm.k_full[(g + 1) & 1]), ((g + 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_s(t, g + 1, cnt[t]);
+              if (t == t_last && b + 2 == z.nb) mma_commit(smem_u32(&sm.q_free));
+            }
+          }
+        }
+        gk += z.nb;
+        ++qi;
+      }
+    }
+  } else {
+    // ---------------- softmax + epilogue: warps 0-3 tile A, warps 4-7 tile B ----------------
+#if VAFA_FWD_PAIR_SETMAXNREG
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+#endif
+    const int t = warp >> 2;
+    const int r = threadIdx.x & 127;
+    const uint32_t lane_base = tbase + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_base + t * kTile;
+    const uint32_t o_addr = lane_base + Cfg::kOCol + t * D;
+    const float c = p.scale_log2;
+    uint32_t gk = 0, cnt = 0, n_ready = 0;
+    bool alive = true;
+    for (uint32_t n = 0; alive; ++n) {
+      const int idx = wq_consume_warp(sm.wq, n, abort_flag);
+      if (idx < 0) break;
+      const WorkItem w = p.items[idx];
+      const PairShape z = pair_shape(w);
+      const int my_nb = z.nb_t[t], my_rows = z.rows_t[t];
+      const int h = w.head;
+      float m_ref = -INFINITY, l = 0.f;
+
+      for (int b = 0; b < my_nb; ++b, ++cnt) {
+        const uint32_t g = gk + b;
+        if (!mbar_wait(smem_u32(&sm.s_full[t][cnt & 1]), (cnt >> 1) & 1, abort_flag)) { alive = false; break; }
+        tc_fence_after();
+        float s[kTile];
+        {
+          uint32_t u0[64], u1[64];
+          tmem_ld64(s_addr, u0);
+          tmem_ld64(s_addr + 64, u1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            s[i] = __uint_as_float(u0[i]);
+            s[64 + i] = __uint_as_float(u1[i]);
+          }
+        }
+        const int lim_tail = w.i_len - 1 - b * kTile;
+        const int lim_diag = w.masked ? (w.diag + t * kTile - b * kTile) : 0x3fffffff;  // for row 0 of the tile
+        const bool masked_block = lim_tail < kTile - 1 || lim_diag < kTile - 1;          // same for the whole tile
+        if (masked_block) {
+          const int lim = min(lim_tail, w.masked ? lim_diag + r : 0x3fffffff);
+#pragma unroll
+          for (int i = 0; i < kTile; ++i) s[i] = (i <= lim) ? s[i] : -INFINITY;
+        }
+        float m8[8];
+#pragma unroll
+        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(s[j2], s[8 + j2], s[16 + j2]);
+#pragma unroll
+        for (int i = 24; i + 16 <= kTile; i += 16) {
+#pragma unroll
+          for (int j2 = 0; j2 < 8; ++j2) m8[j2] = max3(m8[j2], s[i + j2], s[i + 8 + j2]);
+        }
+#pragma unroll
+        for (int j2 = 0; j2 < 8; ++j2) m8[j2] = fmaxf(m8[j2], s[kTile - 8 + j2]);
+        const float mx = max3(max3(m8[0], m8[1], m8[2]), max3(m8[3], m8[4], m8[5]), fmaxf(m8[6], m8[7]));
+        const float m_blk = mx * c;  // c > 0
+        float m_new = fmaxf(m_ref, m_blk);
+        const bool resc = m_new > m_ref + kRescaleThreshold;
+        if (!resc) m_new = m_ref;
+        const float alpha = resc ? ex2(m_ref - m_new) : 1.f;
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        // exponents, row sum and P in two halves of 64 columns (the first half of P is on its way to TMEM while
+        // the second is computed); unmasked blocks take every kPolyPeriod-th pair as a polynomial on the FMA pipe
+        const uint64_t cs2 = pack_f2(c, c), nm2 = pack_f2(-m_use, -m_use);
+        uint64_t sum2[4] = {0ull, 0ull, 0ull, 0ull};
+        auto exps = [&](auto poly_tag) {
+          constexpr bool kPoly = decltype(poly_tag)::value;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int e = 64 * hf + 2 * i;
+              const uint64_t t2 = fma_f2(pack_f2(s[e], s[e + 1]), cs2, nm2);
+              float p0, p1;
+              if (kPoly && (i % kPolyPeriod == kPolyPeriod - 1)) {
+                ex2_poly2(t2, p0, p1);
+              } else {
+                float t0, t1;
+                unpack_f2(t2, t0, t1);
+                p0 = ex2(t0);
+                p1 = ex2(t1);
+              }
+              sum2[i & 3] = add_f2(sum2[i & 3], pack_f2(p0, p1));
+              pk[i] = pack2<T>(p0, p1);
+            }
+            tmem_st32(s_addr + 32 * hf, pk);
+          }
+        };
+        if (masked_block) exps(std::false_type{}); else exps(std::true_type{});
+        {
+          float a0, a1, b0, b1;
+          unpack_f2(add_f2(sum2[0], sum2[1]), a0, a1);
+          unpack_f2(add_f2(sum2[2], sum2[3]), b0, b1);
+          l = l * alpha + ((a0 + a1) + (b0 + b1));
+        }
+        m_ref = m_new;
+        if (b > 0 && __any_sync(0xffffffffu, resc)) {
+          // O may be rescaled once P.V of the previous block is complete; the next one waits for this warp's
+          // arrival below.  No alias in the parity wait: the block after next cannot be issued before it.
+          if (!mbar_wait(smem_u32(&sm.o_done[(g - 1) & 1]), ((g - 1) >> 1) & 1, abort_flag)) { alive = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int c2 = 0; c2 < D / 32; ++c2) {
+            uint32_t tt[32];
+            tmem_ld32(o_addr + c2 * 32, tt);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tt[i] = __float_as_uint(__uint_as_float(tt[i]) * alpha);
+            tmem_st32(o_addr + c2 * 32, tt);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sm.p_full[t][cnt & 1]));
+      }
+      if (!alive) break;
+      gk += z.nb;
+      if (my_rows <= 0) continue;  // no tile B in this item
+
+      // ---- epilogue ----
+      if (my_nb > 0) {
+        if (!mbar_wait(smem_u32(&sm.o_ready[t]), n_ready & 1, abort_flag)) break;
+        ++n_ready;
+        tc_fence_after();
+      }
+      const bool row_ok = r < my_rows;
+      const bool dead = (my_nb == 0) || (l == 0.f);  // a NaN row sum is not a dead row: it goes out as NaN
+      const float inv_l = dead ? 0.f : 1.f / l;
+      const float lse_val = dead ? -INFINITY : m_ref + log2f(l);
+      if (w.partial < 0) {
+        const long long row = (long long)w.o_start + t * kTile + r;
+        T* optr = reinterpret_cast<T*>(p.o) + (row * p.H + h) * D;
+#pragma unroll
+        for (int c2 = 0; c2 < D / 32; ++c2) {
+          uint32_t tt[32];
+          if (my_nb > 0) {
+            tmem_ld32(o_addr + c2 * 32, tt);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tt[i] = 0u;
+          }
+          uint32_t pw[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pw[i] = pack2_out<T>(__uint_as_float(tt[2 * i]) * inv_l, __uint_as_float(tt[2 * i + 1]) * inv_l);
+          store_chunk_coalesced<T>(pw, optr + c2 * 32, (long long)p.H * D, r, my_rows, 4);
+        }
+        if (row_ok) p.lse[row * p.H + h] = lse_val;
+      } else {
+        const long long prow = (long long)w.partial + t * kTile + r;
+        float* optr = p.partial_o + (prow * p.H + h) * D;
+#pragma unroll
+        for (int c2 = 0; c2 < D / 32; ++c2) {
+          uint32_t tt[32];
+          if (my_nb > 0) {
+            tmem_ld32(o_addr + c2 * 32, tt);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) tt[i] = 0u;
+          }
+          if (row_ok) {
+            float4* dst = reinterpret_cast<float4*>(optr + c2 * 32);
+#pragma unroll
+            for (int v4 = 0; v4 < 8; ++v4) {
+              float4 f;
+              f.x = __uint_as_float(tt[4 * v4 + 0]) * inv_l;
+              f.y = __uint_as_float(tt[4 * v4 + 1]) * inv_l;
+              f.z = __uint_as_float(tt[4 * v4 + 2]) * inv_l;
+              f.w = __uint_as_float(tt[4 * v4 + 3]) * inv_l;
+              dst[v4] = f;
+            }
+          }
+        }
+        if (row_ok) p.partial_lse[prow * p.H + h] = lse_val;
+      }
+      // the TMEM reads of O above finish (tcgen05.wait::ld) before this thread's next p_full arrival, and the
+      // next item's first P.V of this tile, which overwrites O, is issued only after that arrival
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (sm.abort_flag != 0) {
+    if (threadIdx.x == 0) report_error(p.status, 1, 111, blockIdx.x);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 200000) { }
+    __syncthreads();
+  }
+  if (warp == 9) tmem_dealloc(tbase, Cfg::kTmemCols);
+}
+
 // ---------------- split-K combine -------------------------------------------------------------
 // Merge the per-split partial outputs (already normalised, fp32) with their log2-domain LSE:
 //   m = max_s lse_s;  w_s = 2^(lse_s - m);  o = sum_s w_s o_s / sum_s w_s;  lse = m + log2 sum_s w_s
@@ -610,6 +1041,15 @@ long long* vafa_trace_buffer = nullptr;
 namespace {
 #endif
 
+// Switch of the two-tile forward kernel (environment variable VAFA_FWD_PAIR=1; off by default, see the kernel).
+bool fwd_pair_enabled() {
+  static const bool on = [] {
+    const char* e = std::getenv("VAFA_FWD_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  return on;
+}
+
 struct FwdWorkspace {
   size_t header, items, combine, plse, po, total;
   SchedCaps caps;
@@ -657,6 +1097,9 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   sp.header = (SchedHeader*)(base + ws.header);
   sp.items = (WorkItem*)(base + ws.items);
   sp.combine = (CombineUnit*)(base + ws.combine);
+  // long query segments: tiles of 256 rows, worked on as two 128-row tiles per CTA
+  const bool pair = fwd_pair_enabled() && (long long)a->total_q > 160LL * a->n_seg;
+  if (pair) sp.tile_rows = 2 * kTile;
   int rc = launch_scheduler(sp, s);
   if (rc) return rc;
 
@@ -686,9 +1129,14 @@ int launch_fwd(const vafa_varlen_args* a, cudaStream_t s, void* scratch = nullpt
   }
 #endif
 
-  const size_t smem = sizeof(FwdSmem<D, false>) + 1024;
-  VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  {
+  if (pair) {
+    const size_t smem = sizeof(PairSmem<D>) + 1024;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_pair_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope scope(kKFwd, s);
+    varlen_fwd_pair_kernel<T, D><<<sms, kPairThreads, smem, s>>>(tq, tk, tv, p);
+  } else {
+    const size_t smem = sizeof(FwdSmem<D, false>) + 1024;
+    VAFA_CUDA_CHECK(cudaFuncSetAttribute(varlen_fwd_kernel<T, D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     LaunchScope scope(kKFwd, s);
     varlen_fwd_kernel<T, D, false><<<sms, kFwdThreads, smem, s>>>(tq, tk, tv, p);
   }
