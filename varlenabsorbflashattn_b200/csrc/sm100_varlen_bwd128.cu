@@ -56,7 +56,21 @@ static_assert(kEw == 8 || kEw == 16, "element-wise warps");
 constexpr int kGroups = kEw / 4;        // column groups of a row
 constexpr int kC = 128 / kGroups;       // score columns per thread
 constexpr int kTmaWarp = kEw, kMmaWarp = kEw + 1;
-constexpr int kThreads = kEw * 32 + 64;  // + 1 TMA warp, 1 MMA warp
+// Registers are granted per four warps, so ten warps leave every thread 168.  With two spare warps the
+// producer / issuer warp group can hand most of its share to the element-wise warp groups (setmaxnreg), which
+// then have 216 each (build with -DVAFA_BWD_SETMAXNREG=1; eight element-wise warps only).
+#ifndef VAFA_BWD_SETMAXNREG
+#define VAFA_BWD_SETMAXNREG 0
+#endif
+static_assert(!VAFA_BWD_SETMAXNREG || kEw == 8, "register hand-over is laid out for eight element-wise warps");
+constexpr int kThreads = kEw * 32 + (VAFA_BWD_SETMAXNREG ? 128 : 64);  // + 1 TMA warp, 1 MMA warp (+ 2 spare)
+#if VAFA_BWD_SETMAXNREG
+#define VAFA_REG_DEC() asm volatile("setmaxnreg.dec.sync.aligned.u32 72;")
+#define VAFA_REG_INC() asm volatile("setmaxnreg.inc.sync.aligned.u32 216;")
+#else
+#define VAFA_REG_DEC()
+#define VAFA_REG_INC()
+#endif
 // one tcgen05.ld for a thread's kC columns
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[64]) { tmem_ld64(taddr, r); }
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[32]) { tmem_ld32(taddr, r); }
@@ -200,7 +214,11 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
   const long long t_begin = clock64();
 #endif
 
-  if (warp == kTmaWarp) {
+  // each setmaxnreg sits inside its own role's branch: after a join the compiler assumes the smaller budget
+  if (warp > kMmaWarp) {
+    VAFA_REG_DEC();  // spare warps of the third warp group
+  } else if (warp == kTmaWarp) {
+    VAFA_REG_DEC();
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       uint32_t gk = 0, qi = 0;
@@ -242,6 +260,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
       }
     }
   } else if (warp == kMmaWarp) {
+    VAFA_REG_DEC();
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -346,6 +365,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
     }
   } else {
     // ---------------- element-wise warps + epilogue (warps 0-7) ----------------
+    VAFA_REG_INC();
     // thread -> outer row r = tid % 128 (TMEM lane; a warp may only touch lane quadrant warp % 4);
     // warps 0-3 take inner columns [0,64) of every block, warps 4-7 columns [64,128)
     const int r = threadIdx.x & 127;
