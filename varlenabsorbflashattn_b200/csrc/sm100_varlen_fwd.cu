@@ -331,7 +331,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         if constexpr (kHalf == 64) {
           uint32_t t0[64];
           tmem_ld64(s_addr, t0);
-          tmem_wait_ld();
+          { TRACE_T0(); tmem_wait_ld(); TRACE_ADD(13); }
 #pragma unroll
           for (int i = 0; i < 64; ++i) s[i] = __uint_as_float(t0[i]);
         } else {
@@ -370,7 +370,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
         // combine with the other half of the row
         sm.xmax[g & 1][half][r] = mx;
         mbar_arrive(pair_bar);
-        if (!mbar_wait(pair_bar, pair_cnt & 1, abort_flag)) { alive = false; break; }
+        { TRACE_T0(); if (!mbar_wait(pair_bar, pair_cnt & 1, abort_flag)) { alive = false; break; } TRACE_ADD(12); }
         ++pair_cnt;
         mx = fmaxf(mx, sm.xmax[g & 1][half ^ 1][r]);
         const float m_blk = mx * c;  // c > 0
@@ -446,7 +446,7 @@ varlen_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_const
             }
           }
         }
-        tmem_wait_st();
+        { TRACE_T0(); tmem_wait_st(); TRACE_ADD(14); }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sm.p_full[g & 1]));
