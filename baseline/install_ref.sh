@@ -1,14 +1,14 @@
 #!/usr/bin/env bash
 # Installs the unmodified reference packages into baseline/_ref (git-ignored; it travels to the GPU
 # box with the working tree).  Needs the reference checkout; run it where that exists:
-#     bash baseline/install_ref.sh [/path/to/reference]
+#     bash baseline/install_ref.sh /path/to/reference
 # The two packages are pure Python (setuptools); they are installed from a scratch copy because
 # setuptools writes egg-info into the source tree and the checkout may be read-only.  The
 # reference's benchmark harness and shape fixtures are not part of its packages; they are copied
 # beside them (tools/, fixtures/) so that the harness can be run against this library
 # (--candidate-varlen varlenabsorbflashattn_b200:packed_varlen_attn).
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:?usage: bash baseline/install_ref.sh /path/to/reference-checkout}"
 HERE="$(cd "$(dirname "$0")" && pwd)"
 DST="$HERE/_ref"
 TMP="$(mktemp -d)"

@@ -2,7 +2,7 @@
 
     python baseline/run_reference_smoke.py [varlen] [absorb]
 
-Needs a B200, the built library and the installed reference (bash baseline/install_ref.sh).  The suites are the
+Needs a B200, the built library and the installed reference (bash baseline/install_ref.sh <reference checkout>).  The suites are the
 unmodified files of the installed packages:
 
   triton_fa_varlen_v2/test_smoke.py       smoke_test(): tiny / cross-block / stage-1 / stage-2 / aligned cases,
@@ -75,7 +75,7 @@ def run_absorb(vb) -> bool:
 
 def main() -> int:
     if not os.path.isdir(os.path.join(HERE, "_ref", "triton_fa_varlen_v2")):
-        print("baseline/_ref is absent: bash baseline/install_ref.sh")
+        print("baseline/_ref is absent: bash baseline/install_ref.sh <reference checkout>")
         return 2
     import varlenabsorbflashattn_b200 as vb
     which = [a for a in sys.argv[1:] if a in ("varlen", "absorb")] or ["varlen", "absorb"]

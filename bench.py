@@ -420,7 +420,7 @@ def absorb_leg(dev, ql, kl, d_q, d_kv, steps, warmup, timed, rank, world, group,
 def compare_leg():
     res = {}
     if not os.path.isdir(os.path.join(REF_DIR, "triton_fa_varlen_v2")):
-        print(json.dumps({"unavailable": "baseline/_ref is missing (bash baseline/install_ref.sh installs the reference there)"}))
+        print(json.dumps({"unavailable": "baseline/_ref is missing (bash baseline/install_ref.sh <reference checkout> installs the reference there)"}))
         return
     sys.path.insert(0, REF_DIR)
     import varlenabsorbflashattn_b200 as vb

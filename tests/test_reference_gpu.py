@@ -37,7 +37,7 @@ _REPORT = {}
 
 def _ref_pkgs():
     if not os.path.isdir(os.path.join(REF_DIR, "triton_fa_varlen_v2")):
-        pytest.skip("baseline/_ref is absent (bash baseline/install_ref.sh)")
+        pytest.skip("baseline/_ref is absent (bash baseline/install_ref.sh <reference checkout>)")
     if REF_DIR not in sys.path:
         sys.path.insert(0, REF_DIR)
     # the reference must be compiled for the GPU here, not run by Triton's CPU interpreter
