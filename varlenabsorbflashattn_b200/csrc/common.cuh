@@ -64,7 +64,8 @@ template <> __device__ __forceinline__ __half from_float<__half>(float x) { retu
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 // bf16 is the upper half of the fp32 pattern, so rounding is an integer add and the packing one
 // byte permute.  This keeps the conversion off the XU pipe (16 lanes/clk/SM), which the kernels
-// need for exp2; cvt.rn.bf16x2 shares that pipe and was costing as much as the exponentials.
+// need for exp2; cvt.rn.bf16x2 shares that pipe and, where every exponential runs there (the backward
+// kernels), costs as much as it saves.
 // Ties round away from zero instead of to even: they differ on exact ties only (1 in 2^16 values).
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   const uint32_t a = __float_as_uint(lo) + 0x8000u;
@@ -82,6 +83,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
 // loops only: its integer rounding turns a NaN whose mantissa is all ones (what the arithmetic units
 // produce) into -0, which is harmless in an operand whose row is marked NaN through its row sum, but would
 // hide a diverged run in an output.  Epilogues run once per tile, so the XU-pipe conversion costs nothing.
+// (The forward kernels also use it for P, see pack_p there.)
 template <typename T> __device__ __forceinline__ uint32_t pack2_out(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2_out<__nv_bfloat16>(float lo, float hi) {
   uint32_t r;

@@ -52,6 +52,14 @@ using namespace ptx;
 #define VAFA_BWD_EW_WARPS 8
 #endif
 constexpr int kEw = VAFA_BWD_EW_WARPS;
+// Rounding of P and dS to the I/O type: pack2 (two adds and a byte permute on the integer pipe) or pack2_out (one
+// conversion on the special-function pipe, which also runs the exponentials).  Measured: the dK/dV kernel, with two
+// roundings per score, is 0.5-1.7 % faster with the conversion; the dQ kernel is level to 1.5 % slower with it.
+template <typename T, bool kDKV>
+__device__ __forceinline__ uint32_t pack_bwd(float lo, float hi) {
+  if constexpr (kDKV) return pack2_out<T>(lo, hi);
+  else return pack2<T>(lo, hi);
+}
 static_assert(kEw == 8 || kEw == 16, "element-wise warps");
 constexpr int kGroups = kEw / 4;        // column groups of a row
 constexpr int kC = 128 / kGroups;       // score columns per thread
@@ -449,7 +457,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
             for (int q2 = 0; q2 < kC / 32; ++q2) {
               uint32_t pp[16];
 #pragma unroll
-              for (int i = 0; i < 16; ++i) pp[i] = pack2<T>(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]);
+              for (int i = 0; i < 16; ++i) pp[i] = pack_bwd<T, kDKV>(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]);
               tmem_st16(x_addr + (grp * (kC / 32) + q2) * 32, pp);
             }
           }
@@ -488,7 +496,7 @@ varlen_bwd128_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __g
               if (!kDKV) y2 = add_f2(y2, nd2);
               float d0, d1;
               unpack_f2(mul_f2(pack_f2(pf[q2 * 32 + 2 * i], pf[q2 * 32 + 2 * i + 1]), y2), d0, d1);
-              dd[i] = pack2<T>(d0, d1);
+              dd[i] = pack_bwd<T, kDKV>(d0, d1);
             }
             // dQ: dS over the scores just consumed (X[g&1]); dK/dV: dS^T over dP^T (Y); in place as above
             tmem_st16((kDKV ? y_addr : x_addr) + (grp * (kC / 32) + q2) * 32, dd);

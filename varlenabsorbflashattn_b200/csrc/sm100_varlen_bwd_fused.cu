@@ -443,7 +443,7 @@ varlen_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
           // P^T packed over A[0,64): my 64 queries become 32 columns at [32 * half, 32 * half + 32)
           uint32_t pp[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) pp[i] = pack2<T>(pf[2 * i], pf[2 * i + 1]);
+          for (int i = 0; i < 32; ++i) pp[i] = pack2_out<T>(pf[2 * i], pf[2 * i + 1]);  // as the dK/dV kernel of the pair
           if (!mbar_wait(pair_bar, pair_cnt & 1, abort_flag)) { alive = false; break; }
           ++pair_cnt;
           tmem_st32(lane_base + kColX + half * 32, pp);
@@ -467,7 +467,7 @@ varlen_bwd_fused_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
             float d0, d1;
             unpack_f2(mul_f2(pack_f2(pf[2 * i], pf[2 * i + 1]),
                              pack_f2(__uint_as_float(ys[2 * i]), __uint_as_float(ys[2 * i + 1]))), d0, d1);
-            dd[i] = pack2<T>(d0, d1);
+            dd[i] = pack2_out<T>(d0, d1);
           }
           // the MMAs that read dS^T of the previous block are complete
           if (g > 0 && !mbar_wait(smem_u32(&sm.ds_free), (g - 1) & 1, abort_flag)) { alive = false; break; }
