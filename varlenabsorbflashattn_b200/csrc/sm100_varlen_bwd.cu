@@ -32,6 +32,15 @@
 namespace vafa {
 namespace {
 
+// Rounding of P and dS to the I/O type in the element-wise phases: the conversion instruction in the kernel that
+// walks query chunks (absorb dU: 4-6 % faster with it, measured), the integer form (see common.cuh) in the one
+// that walks key tiles (absorb dX: level to 2 % slower with the conversion).
+template <typename T, bool kDKV>
+__device__ __forceinline__ uint32_t pack_ew(float lo, float hi) {
+  if constexpr (kDKV) return pack2<T>(lo, hi);
+  else return pack2_out<T>(lo, hi);
+}
+
 using namespace ptx;
 
 // Optional wait-time tracing (build with -DVAFA_TRACE), as in sm100_varlen_fwd.cu.
@@ -485,8 +494,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
               pv[e] = pr;
               dv[e] = ds;
             }
-            pp[i >> 1] = pack2<T>(pv[0], pv[1]);
-            dd[i >> 1] = pack2<T>(dv[0], dv[1]);
+            pp[i >> 1] = pack_ew<T, kDKV>(pv[0], pv[1]);
+            dd[i >> 1] = pack_ew<T, kDKV>(dv[0], dv[1]);
           }
           // 32 fp32 columns become 16 packed columns, written over the first 16 of the columns this
           // thread has just read, so the two halves never touch each other's source columns; the MMA
@@ -539,8 +548,8 @@ varlen_bwd_kernel(const __grid_constant__ CUtensorMap tmap_outer_a, const __grid
               const uint64_t u2 = fma_f2(pack_f2(__uint_as_float(ys[2 * i]), __uint_as_float(ys[2 * i + 1])), s2, pack_f2(d2.x, d2.y));
               float e0, e1;
               unpack_f2(mul_f2(pack_f2(p0, p1), u2), e0, e1);
-              pp[i] = pack2<T>(p0, p1);
-              dd[i] = pack2<T>(e0, e1);
+              pp[i] = pack_ew<T, kDKV>(p0, p1);
+              dd[i] = pack_ew<T, kDKV>(e0, e1);
             }
           };
           if ((skip & 1) == 0) pairs(std::true_type{}); else pairs(std::false_type{});
